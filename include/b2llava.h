@@ -179,6 +179,64 @@ int b2_stream_wait(b2_kv* kv, int index, int32_t* tokens_host, int timeout_ms);
 int b2_batch_begin(b2_model* m, b2_kv* kv, int B, void* stream);
 int b2_batch_set_row(b2_model* m, b2_kv* kv, int slot, int active, const b2_sampling* sampling, int first_token, void* stream);
 
+
+/* ---- layer-list decoders -------------------------------------------------------------------------------------------
+ * A second family of models behind the same handles: decoder-only language models whose configuration LISTS their layers
+ * (first served: Katadra). The residual stream is fp32; every layer adds the LayerNorm of its mixer's output, then, when it
+ * has a feed-forward, the LayerNorm of that; a layer may use an earlier layer's tensors with a state of its own. Mixers:
+ *   B2_MIXER_MAMBA2    in-projection [z | x | B | C | dt], causal depthwise convolution + SiLU over (x, B, C), scalar-decay
+ *                      state-space recurrence per head, SiLU(z) gate, grouped unit-RMS norm, out-projection
+ *   B2_MIXER_PARALLEL  left_scale * attention + right_scale * RWKV time mixing on the same input: the attention has no
+ *                      rotation (unit-RMS q and k, logarithmic query temperature, tanh soft-cap, bucketed distance bias,
+ *                      grouped key/value heads, sigmoid output gate); the RWKV side has token-shift mixes, a low-rank
+ *                      per-channel decay, a bonus for the current token, per-head unit-RMS norm and a SiLU gate
+ * The reference has no such models (its LLMs are HF LLaMA / MPT, llava/model/language_model/); what is shared with the
+ * LLaVA path is everything around the layers: b2_kv slots and lengths, b2_decode_step / b2_decode_greedy / b2_stream_* /
+ * b2_batch_* (CUDA-graph decode step, device-side token selection, host token ring, continuous batching).
+ * compute: B2_COMPUTE_BF16 = bf16 x bf16 -> fp32 matrix products on bf16 weights, everything else fp32;
+ *          B2_COMPUTE_F32  = true fp32 throughout (weights widened at load, FMA products, no TF32). */
+enum { B2_ARCH_LLAVA = 0, B2_ARCH_LAYER_LIST = 1 };
+enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2 };
+enum { B2_COMPUTE_BF16 = 0, B2_COMPUTE_F32 = 1 };
+typedef struct b2_seq_layer_desc {
+    int32_t type;            /* B2_MIXER_* */
+    int32_t weights_of;      /* -1: own tensors; j < this layer: layer j's tensors, own state */
+    int32_t ff;              /* feed-forward width (W_down relu(W_up x)^2); 0 = none */
+    /* B2_MIXER_MAMBA2 */
+    int32_t m_heads, m_vdim, m_state, m_groups, m_conv, m_norm_groups;
+    /* B2_MIXER_PARALLEL, attention side */
+    int32_t a_heads, a_kv_heads, a_dim, a_vdim, a_rel_rows;
+    float a_bias_max, a_scale, a_softcap, a_temp_coef, a_temp_every;
+    /* B2_MIXER_PARALLEL, RWKV side */
+    int32_t r_heads, r_dim, r_decay_rank;
+    float left_scale, right_scale;
+} b2_seq_layer_desc;
+typedef struct b2_seq_model_desc {
+    int32_t width, vocab, n_layers;
+    int32_t compute;         /* B2_COMPUTE_* */
+    float norm_eps;
+    int32_t max_batch;       /* slots a cache of this model may have (rows of a decode step) */
+    int32_t max_rows;        /* most tokens one b2_append_tokens call brings */
+} b2_seq_model_desc;
+int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* layers, b2_model** out);
+/* Tensor names for b2_model_set_weight on such a model: embed, head, final.norm[.b], l<i>.norm1[.b], l<i>.norm2[.b],
+ * l<i>.mix.{in,conv,conv.b,dt_bias,A_log,D,norm,o}, l<i>.mix.left.{q,k,v,g,rel,o}, l<i>.mix.right.{mu.r,mu.k,mu.v,mu.g,mu.w,
+ * r,k,v,g,w1,w2,w0,u,norm,o}, l<i>.mlp.{up,down}; Linear weights are [out, in]. */
+/* Feed the next n tokens of the request in cache slot `slot` (a portion of its prompt, or all of it): the slot's state and
+ * key/value rows continue from its current length, or from an empty sequence when restart != 0 (whatever the slot held
+ * is then dead: nothing needs clearing). want_host lists n_want indices into these n tokens whose logits are written to
+ * logits_out (device or host fp32 [n_want, vocab]); resid_out (device fp32 [n_layers, n, width], nullable) receives the
+ * residual stream after every layer. The logits do not depend on how a prompt is cut into calls, beyond rounding. */
+int b2_append_tokens(b2_model* m, b2_kv* kv, int slot, const int32_t* tokens_host, int n, int restart, const int32_t* want_host,
+                     int n_want, float* logits_out, float* resid_out, void* stream);
+/* b2_decode_step over the slots [slot0, slot0 + B) (b2_decode_step == slot0 0); layer-list models only for slot0 > 0 */
+int b2_decode_step_slots(b2_model* m, b2_kv* kv, const int32_t* tokens, int B, int slot0, void* logits_out, int32_t* next_tokens_out,
+                         void* stream);
+/* Give a slot back: its length becomes 0 (host and device); the next b2_append_tokens on it must restart. */
+int b2_kv_free_slot(b2_kv* kv, int slot, void* stream);
+/* Bytes of device memory one cache of (max_batch, max_seq) takes for this model (state + key/value slabs). */
+int64_t b2_kv_bytes(b2_model* m, int max_batch, int max_seq);
+
 /* ---- single-kernel entry points (unit-level parity tests; same kernels the hot path launches) ----------- */
 int b2_op_gemm(const void* A, int lda, const void* W, int ldw, const void* bias, const void* residual, int ld_res,
                void* out, int ld_out, int out_fp32, int M, int N, int K, int act, int bn_override, void* stream);

@@ -1,0 +1,200 @@
+// Causal softmax attention for layer-list decoders whose positions enter only through the scores: q and k are brought to
+// unit RMS per head (no weight), q carries a temperature that grows with the logarithm of its position, the scaled score is
+// soft-capped with tanh, and a learned bias indexed by a bucket of the distance is added (exact rows for near keys,
+// logarithmic rows up to a far limit, one row beyond; the bucket of every distance is tabulated on the host). Query heads
+// share key/value heads in groups; key and value sizes are free (dk, dv <= 256). Everything is fp32: scores, softmax,
+// the cache. One warp per (row, head [, key split]); a row is a token of a prompt portion or a decode step, and it attends
+// to its slot's cache, which attn_prepare has already extended by the rows of this call.
+#include <math.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b2 {
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// unit = q head (normalise, temperature, in place) | k head (normalise, append) | v head (append)
+__global__ void attn_prepare_kernel(BiasAttnArgs a) {
+    const int units = a.H + 2 * a.G;
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= a.rows * units) return;
+    const int r = w / units, u = w % units;
+    const int pos = a.row_pos[r], slot = a.row_slot[r];
+    if (pos < 0) return;
+    if (u < a.H + a.G) {
+        const bool is_q = u < a.H;
+        float* src = is_q ? a.q + (size_t)r * a.ldq + (size_t)u * a.dk
+                          : const_cast<float*>(a.k) + (size_t)r * a.ldk + (size_t)(u - a.H) * a.dk;
+        float ss = 0.f;
+        for (int d = lane; d < a.dk; d += 32) ss = fmaf(src[d], src[d], ss);
+        ss = warp_sum(ss);
+        float mul = 1.f / sqrtf(ss / (float)a.dk + a.eps);
+        float* dst = src;
+        if (is_q) {
+            mul *= 1.f + a.temp_coef * logf(floorf((float)(pos + 1) / a.temp_every) + 1.f);
+        } else {
+            dst = a.kcache + (((size_t)slot * a.G + (u - a.H)) * a.Smax + pos) * a.dk;
+        }
+        for (int d = lane; d < a.dk; d += 32) dst[d] = src[d] * mul;
+    } else {
+        const int g = u - a.H - a.G;
+        const float* src = a.v + (size_t)r * a.ldv + (size_t)g * a.dv;
+        float* dst = a.vcache + (((size_t)slot * a.G + g) * a.Smax + pos) * a.dv;
+        for (int d = lane; d < a.dv; d += 32) dst[d] = src[d];
+    }
+}
+
+constexpr int AT_WARPS = 4, AT_MAXC = 8;  // dv <= 32 * AT_MAXC
+
+template <bool VEC>
+__global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a) {
+    extern __shared__ float sq[];  // [AT_WARPS][dk]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int w = blockIdx.x * AT_WARPS + warp;
+    const int sp = blockIdx.y;
+    if (w >= a.rows * a.H) return;
+    const int r = w / a.H, h = w % a.H;
+    const int pos = a.row_pos[r];
+    if (pos < 0) return;
+    const int slot = a.row_slot[r], g = h / (a.H / a.G);
+    float* q = sq + warp * a.dk;
+    for (int d = lane; d < a.dk; d += 32) q[d] = a.q[(size_t)r * a.ldq + (size_t)h * a.dk + d];
+    __syncwarp();
+    const float* K = a.kcache + ((size_t)slot * a.G + g) * a.Smax * a.dk;
+    const float* V = a.vcache + ((size_t)slot * a.G + g) * a.Smax * a.dv;
+    int lo = 0, hi = pos + 1;
+    if (a.nsplit > 1) {
+        const int per = ((pos + a.nsplit) / a.nsplit + 31) / 32 * 32;
+        lo = sp * per;
+        hi = min(pos + 1, lo + per);
+    }
+    float m = -INFINITY, l = 0.f, o[AT_MAXC];
+#pragma unroll
+    for (int c = 0; c < AT_MAXC; ++c) o[c] = 0.f;
+    for (int j0 = lo; j0 < hi; j0 += 32) {
+        const int j = j0 + lane;
+        const bool valid = j < hi;
+        float s = -INFINITY;
+        if (valid) {
+            const float* kr = K + (size_t)j * a.dk;
+            float acc = 0.f;
+            if (VEC) {
+                for (int d = 0; d < a.dk; d += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                    const float4 qv = *reinterpret_cast<const float4*>(q + d);
+                    acc = fmaf(qv.x, kv.x, acc); acc = fmaf(qv.y, kv.y, acc); acc = fmaf(qv.z, kv.z, acc); acc = fmaf(qv.w, kv.w, acc);
+                }
+            } else {
+                for (int d = 0; d < a.dk; ++d) acc = fmaf(q[d], kr[d], acc);
+            }
+            s = acc * a.scale;
+            if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+            s += a.rel[(size_t)a.bucket_of[pos - j] * a.H + h];
+        }
+        const float m_new = fmaxf(m, warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);
+        l = fmaf(l, corr, warp_sum(p));
+        m = m_new;
+        const int nk = min(32, hi - j0);
+#pragma unroll
+        for (int c = 0; c < AT_MAXC; ++c) o[c] *= corr;
+        for (int jj = 0; jj < nk; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, p, jj);
+            const float* vr = V + (size_t)(j0 + jj) * a.dv;
+#pragma unroll
+            for (int c = 0; c < AT_MAXC; ++c) {
+                const int d = lane + 32 * c;
+                if (d < a.dv) o[c] = fmaf(pj, vr[d], o[c]);
+            }
+        }
+    }
+    if (a.nsplit > 1) {
+        float* part = a.partial + ((size_t)w * a.nsplit + sp) * (a.dv + 2);
+        if (lane == 0) { part[0] = m; part[1] = l; }
+#pragma unroll
+        for (int c = 0; c < AT_MAXC; ++c) {
+            const int d = lane + 32 * c;
+            if (d < a.dv) part[2 + d] = o[c];
+        }
+    } else {
+        const float inv = 1.f / l;
+#pragma unroll
+        for (int c = 0; c < AT_MAXC; ++c) {
+            const int d = lane + 32 * c;
+            if (d < a.dv) a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = o[c] * inv;
+        }
+    }
+}
+
+// one warp per (row, head): combines the key splits in split order
+__global__ void attn_merge_kernel(BiasAttnArgs a) {
+    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (w >= a.rows * a.H) return;
+    const int r = w / a.H, h = w % a.H;
+    if (a.row_pos[r] < 0) return;
+    const float* part = a.partial + (size_t)w * a.nsplit * (a.dv + 2);
+    float m = -INFINITY;
+    for (int s = 0; s < a.nsplit; ++s) m = fmaxf(m, part[(size_t)s * (a.dv + 2)]);
+    float l = 0.f;
+    for (int s = 0; s < a.nsplit; ++s) {
+        const float* ps = part + (size_t)s * (a.dv + 2);
+        if (ps[1] > 0.f) l = fmaf(ps[1], expf(ps[0] - m), l);
+    }
+    for (int d = lane; d < a.dv; d += 32) {
+        float acc = 0.f;
+        for (int s = 0; s < a.nsplit; ++s) {
+            const float* ps = part + (size_t)s * (a.dv + 2);
+            if (ps[1] > 0.f) acc = fmaf(ps[2 + d], expf(ps[0] - m), acc);
+        }
+        a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = acc / l;
+    }
+}
+
+int check_args(const BiasAttnArgs& a, const char* who) {
+    B2_CHECK_ARG(a.q && a.kcache && a.vcache && a.row_slot && a.row_pos && a.rows > 0, "%s: null argument", who);
+    B2_CHECK_ARG(a.H > 0 && a.G > 0 && a.H % a.G == 0, "%s: %d query heads cannot share %d key/value heads", who, a.H, a.G);
+    B2_CHECK_ARG(a.dk > 0 && a.dk <= 256 && a.dv > 0 && a.dv <= 32 * AT_MAXC, "%s: head sizes %d / %d exceed 256", who, a.dk, a.dv);
+    return 0;
+}
+}  // namespace
+
+int attn_prepare_f32(const BiasAttnArgs& a, cudaStream_t st) {
+    B2_TRY(check_args(a, "attn_prepare"));
+    B2_CHECK_ARG(a.k && a.v && a.temp_every > 0.f, "attn_prepare: null k / v or a non-positive temperature period");
+    const int warps = a.rows * (a.H + 2 * a.G);
+    attn_prepare_kernel<<<(warps + 7) / 8, 256, 0, st>>>(a);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t st) {
+    B2_TRY(check_args(a, "attn_bias"));
+    B2_CHECK_ARG(a.out && a.rel && a.bucket_of, "attn_bias: null argument");
+    B2_CHECK_ARG(a.nsplit >= 1 && (a.nsplit == 1 || a.partial != nullptr), "attn_bias: key splits without scratch");
+    const int warps = a.rows * a.H;
+    const bool vec = a.dk % 4 == 0 && (reinterpret_cast<uintptr_t>(a.kcache) & 15) == 0;
+    dim3 grid((warps + AT_WARPS - 1) / AT_WARPS, a.nsplit);
+    const size_t smem = (size_t)AT_WARPS * a.dk * sizeof(float);
+    if (vec) attn_bias_kernel<true><<<grid, AT_WARPS * 32, smem, st>>>(a);
+    else attn_bias_kernel<false><<<grid, AT_WARPS * 32, smem, st>>>(a);
+    B2_LAUNCH_CHECK();
+    if (a.nsplit > 1) {
+        attn_merge_kernel<<<(warps + 7) / 8, 256, 0, st>>>(a);
+        B2_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
+}  // namespace b2

@@ -238,8 +238,111 @@ struct I32Pack { int32_t v[128]; };
 int set_i32_pairs(int32_t* dst_a, const int32_t* a_host, int32_t* dst_b, const int32_t* b_host, int n, cudaStream_t stream);
 int add_i32(int32_t* x, int n, int delta, cudaStream_t stream);
 int convert_to_bf16(const void* src, int src_dtype, void* dst, int64_t n, cudaStream_t stream);
+int convert_to_f32(const void* src, int src_dtype, float* dst, int64_t n, cudaStream_t stream);  // src on the device
 // out[2I, h]: within each 128-row group g: rows [0,64) = gate[g*64 .. +64), rows [64,128) = up[g*64 .. +64)
 int interleave_gate_up(const void* gate, const void* up, void* out, int I, int h, cudaStream_t stream);
 int store_token(const int32_t* src, int32_t* dst_base, const int32_t* step_counter, int B, cudaStream_t stream);
+
+// =====================================================================================================================
+// Layer-list decoders (seq_engine.cu): fp32 residual stream, recurrent mixers, biased attention with generic head sizes.
+// Rows of one call are described on the device so that a captured decode step follows the cache lengths by itself:
+// a SEGMENT is a run of consecutive rows that belong to one cache slot (a prompt portion: n rows; a decode step: 1 row).
+// =====================================================================================================================
+struct SeqSeg {
+    int slot;   // cache slot (state / key-value slab index)
+    int row0;   // first row of the segment in the call's activation buffers
+    int n;      // rows (0: the slot is idle in this step; nothing of its state is touched)
+    int pos0;   // position of the first row inside its sequence (0: the state starts from zero, whatever the slot held)
+};
+struct RowMap {
+    SeqSeg* segs = nullptr;     // device [nseg]
+    int32_t* row_slot = nullptr;  // device [rows]
+    int32_t* row_pos = nullptr;   // device [rows]; -1 = idle row
+};
+// one segment: rows [0, n) of slot `slot`; its start position is read on the device from len[slot] (and len[slot] += n)
+int rowmap_portion(const RowMap& rm, int32_t* len, int slot, int n, int restart, cudaStream_t stream);
+// B segments of one row each for slots slot0 .. slot0+B-1 at positions len[slot]; with sstate->per_row set, slots whose
+// rows_state entry is not active become idle rows
+int rowmap_decode(const RowMap& rm, const int32_t* len, const SampleState* sstate, const RowState* rows_state, int slot0, int B,
+                  cudaStream_t stream);
+
+// ---- generic Linear on fp32 activations (linear_generic.cu): any M, N, K -----------------------------------------------
+enum { LIN_NONE = 0, LIN_SILU = 1, LIN_SIGMOID = 2, LIN_TANH = 3, LIN_RELU_SQ = 4 };
+struct LinearArgs {
+    const float* A = nullptr; int64_t lda = 0;   // fp32 [M, K]
+    const void* W = nullptr; int64_t ldw = 0;    // [N, K], DT_BF16 or DT_F32
+    int w_dtype = DT_F32;
+    const float* bias = nullptr;                 // fp32 [N] or null
+    float* out = nullptr; int64_t ld_out = 0;    // fp32 [M, N]
+    int M = 0, N = 0, K = 0;
+    int act = LIN_NONE;
+    float alpha = 1.f;                           // out = alpha * act(A W^T + bias) (+ out when accumulate)
+    int accumulate = 0;
+    int round_a = 0;                             // round A to bf16 first (bf16 compute: the product is bf16 x bf16 -> fp32)
+};
+int linear_f32(const LinearArgs& a, cudaStream_t stream);
+
+// ---- fp32 norms and row helpers (norms_f32.cu) ------------------------------------------------------------------------
+// x[r] += LayerNorm(y[r]) * gamma + beta   (normalisation of a sublayer's OUTPUT, added to the residual stream)
+int layernorm_add_f32(float* x, const float* y, const float* gamma, const float* beta, int rows, int cols, float eps, cudaStream_t stream);
+// out[i] = LayerNorm(x[row_index[i]]) * gamma + beta
+int layernorm_gather_f32(const float* x, const int32_t* row_index, const float* gamma, const float* beta, float* out, int rows, int cols,
+                         float eps, cudaStream_t stream);
+// Per row and per group of `group` consecutive channels (cols % group == 0):
+//   gate_first: out = unit_rms(y * silu(z)) * gamma            (state-space mixer: the gate comes before the norm)
+//   otherwise : out = unit_rms(y) * gamma * silu(z)            (RWKV mixer: per-head norm, then weight, then gate)
+int gated_group_rmsnorm_f32(const float* y, int64_t ldy, const float* z, int64_t ldz, const float* gamma, float* out, int64_t ldo, int rows,
+                            int cols, int group, int gate_first, float eps, cudaStream_t stream);
+// x[r, :] = table[tokens[r], :] as fp32; ids outside [0, vocab) give a zero row and raise *err_flag (B2_ERR_TOKEN_RANGE)
+int embed_rows_f32(const int32_t* tokens, const void* table, int table_dtype, float* x, int rows, int cols, int vocab, int* err_flag,
+                   cudaStream_t stream);
+// out[r, c] = a[r, c] * sigmoid(g[r, c])
+int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, float* out, int64_t ldo, int rows, int cols, cudaStream_t stream);
+
+// ---- recurrent mixers (recurrent.cu) ----------------------------------------------------------------------------------
+// Causal depthwise convolution + SiLU with a carried tail: out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]);
+// inputs before the start of the call come from tail[slot][taps-1][C] (zeros when the segment starts a sequence); the tail is
+// replaced by the last taps-1 inputs. taps <= 8.
+int causal_conv_silu_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C,
+                         int taps, const SeqSeg* segs, int nseg, cudaStream_t stream);
+// Token shift: out[s][t, c] = x[t, c] + (x[t-1, c] - x[t, c]) * mu[s][c] for s < n_mix, with x[-1] = prev[slot] (zeros at a sequence
+// start); prev[slot] := the segment's last row. out is [n_mix][rows_total][cols].
+int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out, int64_t out_stride, int cols, int n_mix, const SeqSeg* segs,
+                        int nseg, cudaStream_t stream);
+// Linear recurrence with a diagonal decay over a [key, value] state per head, carried per slot in fp32:
+//   SCAN_SSD : dt = softplus(dt_raw + dt_bias[h]); S = exp(-exp(a_log[h]) dt) S + (dt k) v^T ; y = S^T q + skip[h] v
+//              (q, k: [rows, groups, dk] shared by heads/groups consecutive heads; v: [rows, heads, dv])
+//   SCAN_RWKV: y = (S + diag(bonus[h]) k v^T)^T q ; S = diag(exp(-exp(w_log))) S + k v^T    (q, k, w_log: [rows, heads, dk])
+enum { SCAN_SSD = 0, SCAN_RWKV = 1 };
+struct ScanArgs {
+    int mode = SCAN_SSD;
+    const float *q = nullptr, *k = nullptr, *v = nullptr; int64_t ldq = 0, ldk = 0, ldv = 0;
+    const float* decay_in = nullptr; int64_t ldd = 0;  // SSD: dt_raw [rows, heads]; RWKV: w_log [rows, heads*dk]
+    const float *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr;  // SSD, [heads]
+    const float* bonus = nullptr;                                         // RWKV, [heads, dk]
+    float* state = nullptr;                                               // [slots][heads][dk][dv]
+    float* y = nullptr; int64_t ldy = 0;                                  // [rows, heads*dv]
+    int heads = 0, groups = 0, dk = 0, dv = 0;
+    const SeqSeg* segs = nullptr; int nseg = 0;
+};
+int linear_scan_f32(const ScanArgs& a, cudaStream_t stream);
+
+// ---- attention with unit-RMS q/k, query temperature, tanh soft-cap and a bucketed distance bias (attention_bias.cu) -----
+struct BiasAttnArgs {
+    float* q = nullptr; int64_t ldq = 0;          // [rows, H*dk]: normalised and scaled in place by attn_prepare
+    const float* k = nullptr; int64_t ldk = 0;    // [rows, G*dk] projections of this call's rows
+    const float* v = nullptr; int64_t ldv = 0;    // [rows, G*dv]
+    float* kcache = nullptr; float* vcache = nullptr;  // [slots][G][Smax][dk] / [..][dv] fp32
+    float* out = nullptr; int64_t ldo = 0;        // [rows, H*dv]
+    const float* rel = nullptr;                   // [buckets, H] learned bias
+    const int32_t* bucket_of = nullptr;           // [Smax]: bias row of a distance (built on the host)
+    int H = 0, G = 0, dk = 0, dv = 0, Smax = 0, rows = 0;
+    float eps = 0.f, scale = 1.f, softcap = 0.f;  // softcap <= 0: none
+    float temp_coef = 0.f, temp_every = 1.f;      // q *= 1 + coef * ln(floor((p + 1) / every) + 1)
+    const int32_t* row_slot = nullptr; const int32_t* row_pos = nullptr;
+    float* partial = nullptr; int nsplit = 1;     // split-KV scratch [rows*H*nsplit*(dv+2)] when nsplit > 1
+};
+int attn_prepare_f32(const BiasAttnArgs& a, cudaStream_t stream);  // q/k norms, temperature, cache append
+int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t stream);     // causal softmax attention of every row against its slot's cache
 
 }  // namespace b2

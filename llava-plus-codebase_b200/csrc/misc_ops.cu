@@ -268,6 +268,27 @@ int convert_to_bf16(const void* src, int src_dtype, void* dst, int64_t n, cudaSt
     return 0;
 }
 
+namespace {
+template <typename T>
+__global__ void convert_f32_kernel(const T* __restrict__ src, float* __restrict__ dst, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = (float)src[i];
+}
+}  // namespace
+
+int convert_to_f32(const void* src, int src_dtype, float* dst, int64_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    if (src_dtype == DT_F32) {
+        B2_CUDA_CHECK(cudaMemcpyAsync(dst, src, (size_t)n * 4, cudaMemcpyDefault, stream));
+        return 0;
+    }
+    const int grid = (int)((n + 255) / 256 < 4096 ? (n + 255) / 256 : 4096);
+    if (src_dtype == DT_BF16) convert_f32_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(src), dst, n);
+    else if (src_dtype == DT_F16) convert_f32_kernel<__half><<<grid, 256, 0, stream>>>(reinterpret_cast<const __half*>(src), dst, n);
+    else { set_error("convert_to_f32: unsupported dtype %d", src_dtype); return -1; }
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
 int interleave_gate_up(const void* gate, const void* up, void* out, int I, int h, cudaStream_t stream) {
     B2_CHECK_ARG(I % 64 == 0 && h % 8 == 0, "interleave_gate_up: I %% 64 and h %% 8 must be 0 (I=%d h=%d)", I, h);
     interleave_gate_up_kernel<<<2 * I, 128, 0, stream>>>(reinterpret_cast<const uint4*>(gate),

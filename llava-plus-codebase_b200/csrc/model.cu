@@ -13,9 +13,7 @@
 #include <string>
 #include <vector>
 
-#include "../../include/b2llava.h"
-#include "common.cuh"
-#include "kernels.h"
+#include "engine.h"
 
 namespace b2 {
 
@@ -34,119 +32,9 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
-namespace {
-typedef __nv_bfloat16 bf16;
-
-struct DevBuf {
-    void* p = nullptr;
-    size_t bytes = 0;
-    int alloc(size_t n) {
-        free();
-        if (n == 0) return 0;
-        cudaError_t e = cudaMalloc(&p, n);
-        if (e != cudaSuccess) {
-            p = nullptr;
-            set_error("cudaMalloc(%zu bytes) failed: %s", n, cudaGetErrorString(e));
-            return -2;
-        }
-        bytes = n;
-        return 0;
-    }
-    void free() {
-        if (p) cudaFree(p);
-        p = nullptr;
-        bytes = 0;
-    }
-    template <typename T>
-    T* as() const { return reinterpret_cast<T*>(p); }
-};
-
-struct VitLayer {
-    DevBuf ln1_g, ln1_b, wqkv, bqkv, wo, bo, ln2_g, ln2_b, w1, b1, w2, b2;
-    unsigned qkv_w = 0, qkv_b = 0;  // bit j set: part j (q/k/v) of the fused buffer has arrived
-};
-struct LlamaLayer {
-    DevBuf ln1, wqkv, wo, ln2, wgu, wd;
-    unsigned qkv_parts = 0;
-    DevBuf wqkv8, wo8, wgu8, wd8, s_qkv, s_o, s_gu, s_d;  // e4m3 copies + per-row fp32 scales (b2_model_enable_fp8_decode)
-    DevBuf tmp_gate, tmp_up;  // staging until both halves arrived
-    bool has_gate = false, has_up = false;
-};
-}  // namespace
 }  // namespace b2
 
 using namespace b2;
-
-struct b2_model {
-    b2_model_desc d;
-    int device = 0;
-    std::mutex mu;
-    bool finalized = false;
-    // derived
-    int P = 0, T = 0, kpad = 0, vit_live = 0, vit_hd = 64, hd = 128;
-    // weights
-    DevBuf patch_w, cls, pos, pre_g, pre_b;
-    std::vector<VitLayer> vit;
-    DevBuf p0_w, p0_b, p2_w, p2_b;
-    DevBuf embed, final_norm, lm_head;
-    std::vector<LlamaLayer> ll;
-    // errors detected by kernels (bad token ids / image rows): int[8] in mapped pinned host memory, slot = log2(B2_ERR_*)
-    int* err_host = nullptr;
-    int* err_dev = nullptr;
-    // the workspaces below are shared by every call on this model: a call on stream B must not start before the previous
-    // call's kernels on stream A are done with them (calls on one stream are ordered anyway)
-    cudaEvent_t ws_event = nullptr;
-    cudaStream_t ws_stream = nullptr;
-    bool ws_valid = false;
-    // ViT workspace (per chunk of max_images)
-    DevBuf v_col, v_patch, v_hidden, v_xn, v_qkv, v_attn, v_mlp, v_feats, p_mid, p_done;
-    // LLaMA workspace
-    DevBuf x, xn, qkv, attn, act, last_idx, xlast, logits, splice_idx;
-    // encode_images replays a CUDA graph per chunk size (~190 launches per image, 5-20 us each at B = 1: the host cannot
-    // keep the GPU fed launch by launch). Inputs/outputs are staged through fixed buffers so the captured pointers stay valid.
-    DevBuf enc_pixels, enc_out;
-    std::vector<cudaGraphExec_t> enc_graph;  // index = images in the chunk (0 = unused)
-    std::vector<char> enc_warm;              // an eager run has set the function attributes for this chunk size
-    cudaStream_t enc_stream = nullptr;       // capture is illegal on the legacy default stream: such callers run here
-    cudaEvent_t enc_fork = nullptr, enc_join = nullptr;
-    int enc_launches = 0;                    // kernels in one captured chunk (b2_launch_count bookkeeping)
-    // fp8 decode (BASELINE configs[4]): e4m3 lm_head + scales, quantised activation row buffer + per-token scales
-    bool fp8_decode = false;
-    DevBuf lm_head8, s_head, xq8, xscale;
-};
-
-struct b2_kv {
-    b2_model* m = nullptr;
-    int max_batch = 0, max_seq = 0;
-    DevBuf k, v;  // [L][B][H][Smax][D]
-    DevBuf len_dev, tok, step_counter, out_tokens, attn_partial, attn_counters;
-    DevBuf sk_partial, sk_counters;  // stream-K workspace of the skinny decode GEMM (batch 9..128)
-    std::vector<int32_t> len_host;
-    int out_capacity = 0;  // steps
-    // cached decode-step graph
-    cudaGraphExec_t graph = nullptr;
-    int graph_B = 0;
-    // stream capture is illegal on the legacy default stream (torch's default current stream): decode steps
-    // run on this library-owned stream, ordered against the caller's stream with events
-    unsigned int mega_bar_base = 0;  // value of the grid-barrier counter before the next megakernel launch
-    DevBuf mega_layers, mega_sync;  // MegaLayer[L] table and {bar_count, bar_gen, done_count}
-    DevBuf rope_tab;                // uint32 [max_seq][hd/2]: bf16 (cos, sin) per position for the QKV GEMM's fused RoPE epilogue
-    cudaStream_t own_stream = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
-    int warm_B = 0;  // an eager step has run for this B (function attributes set, driver entry points resolved)
-    // token selection state (sampling.cu) + the host-visible token ring of the streaming decode API
-    DevBuf sstate;                 // SampleState on the device
-    SampleState samp_host = {};    // what was last written there (pub_counter / done excluded: the device advances them)
-    bool samp_valid = false;
-    int32_t* ring_host = nullptr;  // cudaHostAlloc(mapped) [ring_cap][max_batch]; entry = tag << 20 | token
-    int32_t* ring_dev = nullptr;
-    int ring_cap = 0;
-    int epoch = 0;                 // generations started on this cache (tag = 1 + epoch % 2047)
-    int stream_B = 0, stream_tag = 0, stream_scheduled = 0;  // streaming generation in progress: tokens scheduled so far
-    DevBuf rows_dev;               // RowState[max_batch] (continuous batching)
-    std::vector<RowState> rows_host;
-    size_t layer_stride() const { return (size_t)max_batch * m->d.heads * max_seq * m->hd; }
-};
 
 namespace {
 
@@ -495,6 +383,7 @@ int encode_chunk(b2_model* m, const void* pixels, int n, void* out, cudaStream_t
 
 // one decode step on kv-owned buffers: tok -> logits (m->logits) -> argmax -> tok, out_tokens[step], len += 1
 int decode_step_launch(b2_model* m, b2_kv* kv, int B, cudaStream_t st) {
+    if (m->arch == B2_ARCH_LAYER_LIST) return seq_decode_launch(m, kv, B, 0, st);
     const b2_model_desc& d = m->d;
     const int h = d.hidden, I = d.inter, H = d.heads, V = d.vocab;
     const int nsplit = decode_nsplit(B, H, kv->max_seq);
@@ -694,7 +583,7 @@ int decode_step_mega(b2_model* m, b2_kv* kv, int B, cudaStream_t st) {
 
 int decode_step_run(b2_model* m, b2_kv* kv, int B, cudaStream_t st) {
     // B <= 8: one persistent cooperative launch per token (no graph needed: launches queue asynchronously)
-    if (use_mega(m, B)) return decode_step_mega(m, kv, B, st);
+    if (m->arch == B2_ARCH_LLAVA && use_mega(m, B)) return decode_step_mega(m, kv, B, st);
     if (kv->warm_B != B) {
         // first step for this batch size runs eagerly: sets function attributes, resolves driver entry points
         if (kv->graph) { cudaGraphExecDestroy(kv->graph); kv->graph = nullptr; kv->graph_B = 0; }
@@ -708,6 +597,7 @@ int decode_step_run(b2_model* m, b2_kv* kv, int B, cudaStream_t st) {
         B2_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         const unsigned long long launches_before = g_launch_count;
         int r = decode_step_launch(m, kv, B, st);
+        kv->seq_graph_launches = (int)(g_launch_count - launches_before);
         g_launch_count = launches_before;  // capture records launches, it does not run them
         cudaError_t e = cudaStreamEndCapture(st, &graph);
         if (r != 0) { if (graph) cudaGraphDestroy(graph); return r; }
@@ -718,6 +608,7 @@ int decode_step_run(b2_model* m, b2_kv* kv, int B, cudaStream_t st) {
         kv->graph_B = B;
     }
     B2_CUDA_CHECK(cudaGraphLaunch(kv->graph, st));
+    if (m->arch == B2_ARCH_LAYER_LIST) { g_launch_count += (unsigned long long)kv->seq_graph_launches; return 0; }
     // kernels per step: embed + L*(qkv, attn, o, gate/up, down [+2 norms when B>8]) + head(+norm) + sample_publish
     const bool small = !use_skinny(kv, B) && B <= 8 && gemv_fits(B, m->d.hidden, m->d.inter, ACT_NONE) &&
                        gemv_fits(B, m->d.vocab, m->d.hidden, ACT_NONE);
@@ -726,18 +617,44 @@ int decode_step_run(b2_model* m, b2_kv* kv, int B, cudaStream_t st) {
     return 0;
 }
 
-// makes `dev` current for the duration of an ABI call and restores the caller's device afterwards
-struct DeviceGuard {
-    int prev = -1;
-    explicit DeviceGuard(int dev) {
-        if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
-        if (prev != dev) cudaSetDevice(dev); else prev = -1;
-    }
-    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
-    DeviceGuard(const DeviceGuard&) = delete;
-    DeviceGuard& operator=(const DeviceGuard&) = delete;
-};
+}  // namespace
 
+namespace b2 {
+int kv_alloc_common(b2_kv* kv) {
+    const int max_batch = kv->max_batch, max_seq = kv->max_seq;
+    B2_TRY(kv->len_dev.alloc((size_t)max_batch * 4));
+    B2_TRY(kv->tok.alloc((size_t)max_batch * 4));
+    B2_TRY(kv->step_counter.alloc(4));
+    kv->out_capacity = max_seq;
+    B2_TRY(kv->out_tokens.alloc((size_t)kv->out_capacity * max_batch * 4));
+    kv->ring_cap = max_seq;
+    B2_TRY(kv->sstate.alloc(sizeof(SampleState)));
+    B2_TRY(kv->rows_dev.alloc((size_t)max_batch * sizeof(RowState)));
+    cudaMemset(kv->sstate.p, 0, sizeof(SampleState));
+    cudaMemset(kv->rows_dev.p, 0, (size_t)max_batch * sizeof(RowState));
+    kv->rows_host.assign(max_batch, RowState{});
+    if (cudaHostAlloc(reinterpret_cast<void**>(&kv->ring_host), (size_t)kv->ring_cap * max_batch * 4, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void**>(&kv->ring_dev), kv->ring_host, 0) != cudaSuccess) {
+        set_error("b2_kv_create: cannot allocate the pinned token ring (%d x %d)", kv->ring_cap, max_batch);
+        cudaGetLastError();
+        return -2;
+    }
+    memset(kv->ring_host, 0, (size_t)kv->ring_cap * max_batch * 4);
+    cudaMemset(kv->len_dev.p, 0, (size_t)max_batch * 4);
+    cudaMemset(kv->tok.p, 0, (size_t)max_batch * 4);
+    cudaMemset(kv->step_counter.p, 0, 4);
+    kv->len_host.assign(max_batch, 0);
+    return 0;
+}
+int model_common_init(b2_model* m) {
+    if (m->err_host == nullptr) {
+        B2_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&m->err_host), 8 * sizeof(int), cudaHostAllocMapped));
+        memset(m->err_host, 0, 8 * sizeof(int));
+        B2_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&m->err_dev), m->err_host, 0));
+        B2_CUDA_CHECK(cudaEventCreateWithFlags(&m->ws_event, cudaEventDisableTiming));
+    }
+    return 0;
+}
 // Cross-stream ordering of the shared model workspaces (see b2_model::ws_event). Caller holds the model lock.
 int ws_enter(b2_model* m, cudaStream_t st) {
     if (m->ws_valid && m->ws_stream != st) B2_CUDA_CHECK(cudaStreamWaitEvent(st, m->ws_event, 0));
@@ -749,8 +666,7 @@ int ws_leave(b2_model* m, cudaStream_t st) {
     m->ws_valid = true;
     return 0;
 }
-
-}  // namespace
+}  // namespace b2
 
 // ==========================================================================================================
 // C ABI
@@ -810,6 +726,7 @@ int b2_model_set_weight(b2_model* m, const char* hf_key, const void* ptr, const 
     B2_CHECK_ARG(dtype == DT_BF16 || dtype == DT_F16 || dtype == DT_F32, "b2_model_set_weight: bad dtype %d", dtype);
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
+    if (m->arch == B2_ARCH_LAYER_LIST) return seq_set_weight(m, hf_key, ptr, shape, ndim, dtype);
     std::string k(hf_key);
     const int h = m->d.hidden, V = m->d.vocab, D = m->d.vit_hidden;
     int r = -1;
@@ -855,6 +772,12 @@ int b2_model_finalize(b2_model* m) {
     B2_CHECK_ARG(m != nullptr, "b2_model_finalize: null model");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
+    if (m->arch == B2_ARCH_LAYER_LIST) {
+        B2_TRY(seq_finalize(m));
+        B2_TRY(model_common_init(m));
+        m->finalized = true;
+        return 0;
+    }
     const b2_model_desc& d = m->d;
     // completeness
     std::string missing;
@@ -895,12 +818,7 @@ int b2_model_finalize(b2_model* m) {
             set_error("b2_model_finalize: decoder layer %zu is missing q/k/v projections (mask %u of 7)", i, m->ll[i].qkv_parts);
             return -3;
         }
-    if (m->err_host == nullptr) {
-        B2_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&m->err_host), 8 * sizeof(int), cudaHostAllocMapped));
-        memset(m->err_host, 0, 8 * sizeof(int));
-        B2_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&m->err_dev), m->err_host, 0));
-        B2_CUDA_CHECK(cudaEventCreateWithFlags(&m->ws_event, cudaEventDisableTiming));
-    }
+    B2_TRY(model_common_init(m));
     // workspaces
     const int D = d.vit_hidden, I = d.vit_inter, h = d.hidden;
     const size_t vrows = (size_t)d.max_images * m->T, prow = (size_t)d.max_images * m->P;
@@ -947,6 +865,7 @@ int b2_model_destroy(b2_model* m) {
                      &m->v_qkv, &m->v_attn, &m->v_mlp, &m->v_feats, &m->p_mid, &m->p_done, &m->enc_pixels, &m->enc_out, &m->x, &m->xn, &m->qkv, &m->attn,
                      &m->act, &m->last_idx, &m->xlast, &m->logits, &m->splice_idx, &m->lm_head8, &m->s_head, &m->xq8, &m->xscale};
     for (DevBuf* b : top) b->free();
+    seq_model_free(m);
     for (VitLayer& L : m->vit) {
         DevBuf* bs[12] = {&L.ln1_g, &L.ln1_b, &L.wqkv, &L.bqkv, &L.wo, &L.bo, &L.ln2_g, &L.ln2_b, &L.w1, &L.b1, &L.w2, &L.b2};
         for (DevBuf* b : bs) b->free();
@@ -965,6 +884,7 @@ int b2_model_destroy(b2_model* m) {
 int b2_model_enable_fp8_decode(b2_model* m) {
     B2_CHECK_ARG(m != nullptr, "b2_model_enable_fp8_decode: null model");
     B2_CHECK_ARG(m->finalized, "b2_model_enable_fp8_decode: model not finalized");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA, "b2_model_enable_fp8_decode: not part of a layer-list model");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
     if (m->fp8_decode) return 0;
@@ -996,21 +916,29 @@ int b2_kv_create(b2_model* m, int max_batch, int max_seq, b2_kv** out) {
     B2_CHECK_ARG(max_batch >= 1 && max_batch <= m->d.max_batch, "b2_kv_create: max_batch %d exceeds model max_batch %d",
                  max_batch, m->d.max_batch);
     B2_CHECK_ARG(max_seq >= 1, "b2_kv_create: max_seq must be positive");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA || m->finalized, "b2_kv_create: finalize the model first");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
     b2_kv* kv = new b2_kv();
     kv->m = m;
     kv->max_batch = max_batch;
     kv->max_seq = max_seq;
-    const size_t per = (size_t)m->d.layers * kv->layer_stride() * 2;
-    int r = 0;
-    if ((r = kv->k.alloc(per)) != 0 || (r = kv->v.alloc(per)) != 0 ||
-        (r = kv->len_dev.alloc((size_t)max_batch * 4)) != 0 || (r = kv->tok.alloc((size_t)max_batch * 4)) != 0 ||
-        (r = kv->step_counter.alloc(4)) != 0) {
+    int r = kv_alloc_common(kv);
+    if (r == 0 && m->arch == B2_ARCH_LAYER_LIST) r = seq_kv_alloc(kv);
+    if (r != 0) {
         b2_kv_destroy(kv);
         return r;
     }
-    kv->out_capacity = max_seq;
+    if (m->arch == B2_ARCH_LAYER_LIST) {
+        B2_CUDA_CHECK(cudaDeviceSynchronize());  // the zero-fills ran on the legacy stream (see below)
+        *out = kv;
+        return 0;
+    }
+    const size_t per = (size_t)m->d.layers * kv->layer_stride() * 2;
+    if ((r = kv->k.alloc(per)) != 0 || (r = kv->v.alloc(per)) != 0) {
+        b2_kv_destroy(kv);
+        return r;
+    }
     const int max_split = 64;
     {
         std::vector<MegaLayer> tbl(m->d.layers);
@@ -1028,8 +956,7 @@ int b2_kv_create(b2_model* m, int max_batch, int max_seq, b2_kv** out) {
         cudaMemcpy(kv->mega_layers.p, tbl.data(), tbl.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice);
         cudaMemset(kv->mega_sync.p, 0, 64);
     }
-    if ((r = kv->out_tokens.alloc((size_t)kv->out_capacity * max_batch * 4)) != 0 ||
-        (r = kv->attn_partial.alloc(((size_t)max_batch * m->d.heads * max_split + 1024) * (128 + 2) * 4)) != 0 ||
+    if ((r = kv->attn_partial.alloc(((size_t)max_batch * m->d.heads * max_split + 1024) * (128 + 2) * 4)) != 0 ||
         (r = kv->attn_counters.alloc((size_t)max_batch * m->d.heads * 4)) != 0) {
         b2_kv_destroy(kv);
         return r;
@@ -1050,27 +977,8 @@ int b2_kv_create(b2_model* m, int max_batch, int max_seq, b2_kv** out) {
         }
         cudaMemset(kv->sk_counters.p, 0, gemm_skinny_counter_bytes(nmax));
     }
-    kv->ring_cap = max_seq;
-    if ((r = kv->sstate.alloc(sizeof(SampleState))) != 0 || (r = kv->rows_dev.alloc((size_t)max_batch * sizeof(RowState))) != 0) {
-        b2_kv_destroy(kv);
-        return r;
-    }
-    cudaMemset(kv->sstate.p, 0, sizeof(SampleState));
-    cudaMemset(kv->rows_dev.p, 0, (size_t)max_batch * sizeof(RowState));
-    kv->rows_host.assign(max_batch, RowState{});
-    if (cudaHostAlloc(reinterpret_cast<void**>(&kv->ring_host), (size_t)kv->ring_cap * max_batch * 4, cudaHostAllocMapped) != cudaSuccess ||
-        cudaHostGetDevicePointer(reinterpret_cast<void**>(&kv->ring_dev), kv->ring_host, 0) != cudaSuccess) {
-        set_error("b2_kv_create: cannot allocate the pinned token ring (%d x %d)", kv->ring_cap, max_batch);
-        cudaGetLastError();
-        b2_kv_destroy(kv);
-        return -2;
-    }
-    memset(kv->ring_host, 0, (size_t)kv->ring_cap * max_batch * 4);
     cudaMemset(kv->k.p, 0, per);
     cudaMemset(kv->v.p, 0, per);
-    cudaMemset(kv->len_dev.p, 0, (size_t)max_batch * 4);
-    cudaMemset(kv->tok.p, 0, (size_t)max_batch * 4);
-    cudaMemset(kv->step_counter.p, 0, 4);
     cudaMemset(kv->attn_counters.p, 0, (size_t)max_batch * m->d.heads * 4);
     if ((r = kv->rope_tab.alloc((size_t)max_seq * (m->hd / 2) * sizeof(uint32_t))) != 0 ||
         (r = rope_table_build(kv->rope_tab.p, max_seq, m->hd, m->d.rope_theta, nullptr)) != 0) {
@@ -1081,7 +989,6 @@ int b2_kv_create(b2_model* m, int max_batch, int max_seq, b2_kv** out) {
     // is NOT ordered against it: a prefill issued right after this call would race with the zero-fill of the cache it writes
     // (seen in scripts/decode_ab.py FRESHKV=1: different tokens on a cache that was created a moment earlier).
     B2_CUDA_CHECK(cudaDeviceSynchronize());
-    kv->len_host.assign(max_batch, 0);
     *out = kv;
     return 0;
 }
@@ -1113,6 +1020,7 @@ int b2_kv_destroy(b2_kv* kv) {
     if (kv->own_stream) cudaStreamDestroy(kv->own_stream);
     if (kv->ev_fork) cudaEventDestroy(kv->ev_fork);
     if (kv->ev_join) cudaEventDestroy(kv->ev_join);
+    seq_kv_free(kv);
     DevBuf* bs[] = {&kv->k, &kv->v, &kv->len_dev, &kv->tok, &kv->step_counter, &kv->out_tokens, &kv->attn_partial,
                     &kv->attn_counters, &kv->mega_layers, &kv->mega_sync, &kv->sk_partial, &kv->sk_counters, &kv->sstate, &kv->rows_dev, &kv->rope_tab};
     for (DevBuf* b : bs) b->free();
@@ -1130,6 +1038,7 @@ int b2_kv_lengths(b2_kv* kv, int32_t* lens_host, int n) {
 int b2_vit_encode(b2_model* m, const void* pixels, int B, void* out_feats, void* stream) {
     B2_CHECK_ARG(m && pixels && out_feats && B >= 1, "b2_vit_encode: bad argument");
     B2_CHECK_ARG(m->finalized, "b2_vit_encode: model not finalized");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA, "b2_vit_encode: not part of a layer-list model");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -1146,6 +1055,7 @@ int b2_vit_encode(b2_model* m, const void* pixels, int B, void* out_feats, void*
 int b2_project(b2_model* m, const void* feats, int rows, void* out, void* stream) {
     B2_CHECK_ARG(m && feats && out && rows >= 1, "b2_project: bad argument");
     B2_CHECK_ARG(m->finalized, "b2_project: model not finalized");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA, "b2_project: not part of a layer-list model");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -1157,6 +1067,7 @@ int b2_project(b2_model* m, const void* feats, int rows, void* out, void* stream
 int b2_encode_images(b2_model* m, const void* pixels, int B, void* out, void* stream) {
     B2_CHECK_ARG(m && pixels && out && B >= 1, "b2_encode_images: bad argument");
     B2_CHECK_ARG(m->finalized, "b2_encode_images: model not finalized");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA, "b2_encode_images: not part of a layer-list model");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -1175,6 +1086,7 @@ int b2_splice(b2_model* m, const int32_t* src_index, const void* image_feats, in
     B2_CHECK_ARG(m && src_index && embeds_out && rows >= 1 && n_feat_rows >= 0, "b2_splice: bad argument");
     B2_CHECK_ARG(image_feats != nullptr || n_feat_rows == 0, "b2_splice: n_feat_rows=%d without image_feats", n_feat_rows);
     B2_CHECK_ARG(m->finalized, "b2_splice: model not finalized");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA, "b2_splice: not part of a layer-list model");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
     return splice_embed(src_index, m->embed.p, image_feats, embeds_out, rows, m->d.hidden, m->d.vocab, n_feat_rows,
@@ -1185,6 +1097,7 @@ int b2_splice_ids(b2_model* m, const int64_t* input_ids, int B, int Lt, int k_pe
                   const void* image_feats, int S, void* embeds_out, void* stream) {
     B2_CHECK_ARG(m && input_ids && feat_offsets_host && embeds_out, "b2_splice_ids: null argument");
     B2_CHECK_ARG(m->finalized, "b2_splice_ids: model not finalized");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA, "b2_splice_ids: not part of a layer-list model");
     B2_CHECK_ARG(B >= 1 && S >= 1 && (size_t)B * S <= (size_t)m->d.max_batch * m->d.max_seq,
                  "b2_splice_ids: B*S=%d exceeds the workspace (%d rows)", B * S, m->d.max_batch * m->d.max_seq);
     B2_CHECK_ARG(image_feats != nullptr || n_img == 0, "b2_splice_ids: image slots without image_feats");
@@ -1225,6 +1138,7 @@ int b2_prefill_slots(b2_model* m, b2_kv* kv, const void* embeds, const int32_t* 
                      void* logits_out, int logits_mode, void* stream) {
     B2_CHECK_ARG(m && kv && embeds && kv->m == m, "b2_prefill: bad handle");
     B2_CHECK_ARG(m->finalized, "b2_prefill: model not finalized");
+    B2_CHECK_ARG(m->arch == B2_ARCH_LLAVA, "b2_prefill: not part of a layer-list model");
     B2_CHECK_ARG(B >= 1 && slot0 >= 0 && slot0 + B <= kv->max_batch && S >= 1 && S <= kv->max_seq,
                  "b2_prefill: B=%d S=%d slot0=%d exceed the KV cache (max_batch=%d max_seq=%d)", B, S, slot0, kv->max_batch, kv->max_seq);
     B2_CHECK_ARG((size_t)B * S <= (size_t)m->d.max_batch * m->d.max_seq,
@@ -1327,31 +1241,40 @@ static bool is_device_pointer(const void* p) {
 
 int b2_decode_step(b2_model* m, b2_kv* kv, const int32_t* tokens, int B, void* logits_out, int32_t* next_tokens_out,
                    void* stream) {
+    return b2_decode_step_slots(m, kv, tokens, B, 0, logits_out, next_tokens_out, stream);
+}
+
+int b2_decode_step_slots(b2_model* m, b2_kv* kv, const int32_t* tokens, int B, int slot0, void* logits_out, int32_t* next_tokens_out,
+                         void* stream) {
     B2_CHECK_ARG(m && kv && tokens && kv->m == m, "b2_decode_step: bad handle");
     B2_CHECK_ARG(m->finalized, "b2_decode_step: model not finalized");
-    B2_CHECK_ARG(B >= 1 && B <= kv->max_batch, "b2_decode_step: B=%d exceeds cache batch %d", B, kv->max_batch);
+    B2_CHECK_ARG(B >= 1 && slot0 >= 0 && slot0 + B <= kv->max_batch, "b2_decode_step: slots %d..%d exceed cache batch %d", slot0, slot0 + B - 1,
+                 kv->max_batch);
+    B2_CHECK_ARG(slot0 == 0 || m->arch == B2_ARCH_LAYER_LIST, "b2_decode_step: a slot offset needs a layer-list model");
     std::lock_guard<std::mutex> lk(m->mu);
     DeviceGuard dg(m->device);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    for (int b = 0; b < B; ++b)
+    for (int b = slot0; b < slot0 + B; ++b)
         B2_CHECK_ARG(kv->len_host[b] >= 1 && kv->len_host[b] < kv->max_seq,
                      "b2_decode_step: sample %d has cache length %d (capacity %d; prefill first)", b, kv->len_host[b],
                      kv->max_seq);
     B2_TRY(ws_enter(m, st));
-    B2_TRY(copy_tokens_in(kv, tokens, B, st));
+    B2_CUDA_CHECK(cudaMemcpyAsync(kv->tok.as<int32_t>() + slot0, tokens, (size_t)B * 4, cudaMemcpyDefault, st));
     B2_CUDA_CHECK(cudaMemsetAsync(kv->step_counter.p, 0, 4, st));
     B2_TRY(set_greedy_unpublished(kv, st));
     cudaStream_t run = nullptr;
     B2_TRY(fork_stream(kv, st, &run));
-    B2_TRY(decode_step_run(m, kv, B, run));
+    if (slot0 == 0) B2_TRY(decode_step_run(m, kv, B, run));
+    else B2_TRY(seq_decode_launch(m, kv, B, slot0, run));  // the captured step covers slots from 0: others run launch by launch
     B2_TRY(join_stream(kv, st, run));
-    for (int b = 0; b < B; ++b) kv->len_host[b]++;
+    for (int b = slot0; b < slot0 + B; ++b) kv->len_host[b]++;
     if (logits_out)
         B2_CUDA_CHECK(cudaMemcpyAsync(logits_out, m->logits.p, (size_t)B * m->d.vocab * 4, cudaMemcpyDefault, st));
     if (next_tokens_out)
-        B2_CUDA_CHECK(cudaMemcpyAsync(next_tokens_out, kv->tok.p, (size_t)B * 4, cudaMemcpyDefault, st));
+        B2_CUDA_CHECK(cudaMemcpyAsync(next_tokens_out, kv->tok.as<int32_t>() + slot0, (size_t)B * 4, cudaMemcpyDefault, st));
     B2_TRY(ws_leave(m, st));
-    if (next_tokens_out && !is_device_pointer(next_tokens_out)) B2_CUDA_CHECK(cudaStreamSynchronize(st));
+    if ((next_tokens_out && !is_device_pointer(next_tokens_out)) || (logits_out && !is_device_pointer(logits_out)))
+        B2_CUDA_CHECK(cudaStreamSynchronize(st));
     return 0;
 }
 

@@ -1,0 +1,233 @@
+// Recurrent mixers of the layer-list decoders: causal depthwise convolution with a carried tail, RWKV token shift, and the
+// linear recurrence with a diagonal decay over a per-head [key, value] state (state-space and RWKV forms). One code path
+// serves a portion of a prompt (n rows of one slot) and a decode step (one row of each of B slots): the rows come as
+// segments (kernels.h, SeqSeg). State, decays, step sizes and sums are fp32; a segment whose pos0 is 0 starts from zero
+// state whatever its slot held before, so a slot that is handed to a new request needs no clearing.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b2 {
+namespace {
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// ---- causal depthwise convolution + SiLU: one thread per channel walks its segment with the window in registers --------
+constexpr int CONV_MAX_TAPS = 8, CONV_UNROLL = 8;
+__global__ void __launch_bounds__(128) causal_conv_silu_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ w,
+                                                               const float* __restrict__ bias, float* __restrict__ tail, float* __restrict__ out,
+                                                               int64_t ld_out, int C, int taps, const SeqSeg* __restrict__ segs) {
+    const SeqSeg sg = segs[blockIdx.y];
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C || sg.n <= 0) return;
+    // Window and taps are kept right-aligned in arrays of CONV_MAX_TAPS (all indices static): entry CONV_MAX_TAPS-1 is the
+    // current token, the unused leading entries carry zero weights.
+    float wt[CONV_MAX_TAPS], win[CONV_MAX_TAPS];
+#pragma unroll
+    for (int jp = 0; jp < CONV_MAX_TAPS; ++jp) {
+        const int tj = jp - (CONV_MAX_TAPS - taps);
+        wt[jp] = tj >= 0 ? w[(size_t)c * taps + tj] : 0.f;
+        win[jp] = 0.f;
+    }
+    float* tl = tail + (size_t)sg.slot * (taps - 1) * C + c;
+    if (sg.pos0 > 0) {
+#pragma unroll
+        for (int jp = 1; jp < CONV_MAX_TAPS; ++jp) {
+            const int j = jp - (CONV_MAX_TAPS - (taps - 1));
+            if (j >= 0) win[jp] = tl[(size_t)j * C];
+        }
+    }
+    const float b = bias[c];
+    const float* ip = in + (size_t)sg.row0 * ld_in + c;
+    float* op = out + (size_t)sg.row0 * ld_out + c;
+    for (int t0 = 0; t0 < sg.n; t0 += CONV_UNROLL) {
+        float v[CONV_UNROLL];
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) v[u] = t0 + u < sg.n ? ip[(size_t)(t0 + u) * ld_in] : 0.f;
+#pragma unroll
+        for (int u = 0; u < CONV_UNROLL; ++u) {
+            if (t0 + u < sg.n) {
+#pragma unroll
+                for (int jp = 0; jp < CONV_MAX_TAPS - 1; ++jp) win[jp] = win[jp + 1];
+                win[CONV_MAX_TAPS - 1] = v[u];
+                float acc = b;
+#pragma unroll
+                for (int jp = 0; jp < CONV_MAX_TAPS; ++jp) acc = fmaf(wt[jp], win[jp], acc);
+                op[(size_t)(t0 + u) * ld_out] = silu_f(acc);
+            }
+        }
+    }
+#pragma unroll
+    for (int jp = 1; jp < CONV_MAX_TAPS; ++jp) {
+        const int j = jp - (CONV_MAX_TAPS - (taps - 1));
+        if (j >= 0) tl[(size_t)j * C] = win[jp];
+    }
+}
+
+// ---- token shift: out[s][t] = x[t] + (x[t-1] - x[t]) * mu[s] ------------------------------------------------------------
+constexpr int SHIFT_MAX_MIX = 8;
+__global__ void __launch_bounds__(128) token_shift_mix_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* __restrict__ prev,
+                                                              float* __restrict__ out, int64_t out_stride, int cols, int n_mix,
+                                                              const SeqSeg* __restrict__ segs) {
+    const SeqSeg sg = segs[blockIdx.y];
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols || sg.n <= 0) return;
+    float m[SHIFT_MAX_MIX];
+#pragma unroll
+    for (int s = 0; s < SHIFT_MAX_MIX; ++s) m[s] = s < n_mix ? mu[(size_t)s * cols + c] : 0.f;
+    float last = sg.pos0 > 0 ? prev[(size_t)sg.slot * cols + c] : 0.f;
+    for (int t0 = 0; t0 < sg.n; t0 += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = t0 + u < sg.n ? x[(size_t)(sg.row0 + t0 + u) * cols + c] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (t0 + u < sg.n) {
+                const float d = last - v[u];
+#pragma unroll
+                for (int s = 0; s < SHIFT_MAX_MIX; ++s)
+                    if (s < n_mix) out[(size_t)s * out_stride + (size_t)(sg.row0 + t0 + u) * cols + c] = fmaf(d, m[s], v[u]);
+                last = v[u];
+            }
+        }
+    }
+    prev[(size_t)sg.slot * cols + c] = last;
+}
+
+// ---- linear recurrence ------------------------------------------------------------------------------------------------
+// Block = 32 value columns (threadIdx.x) x KS key slices (threadIdx.y) of one head of one segment. A thread keeps KPT keys
+// of its column's state in registers. Tokens are staged TT at a time into shared memory with the per-token preparation done
+// while staging (step size, decay, dt-scaled key), then walked in order; the KS partial dot products of a token meet in a
+// double-buffered shared array (one barrier per token).
+constexpr int KPT = 16, TT = 16;
+
+template <int MODE>
+__global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
+    extern __shared__ float sm[];
+    const SeqSeg sg = a.segs[blockIdx.z];
+    if (sg.n <= 0) return;
+    const int h = blockIdx.y, j = blockIdx.x * 32 + threadIdx.x, ks = threadIdx.y, KS = blockDim.y;
+    const int dk = a.dk, dv = a.dv, dkp = KS * KPT;
+    const int tid = threadIdx.y * 32 + threadIdx.x, nthr = KS * 32;
+    float* sQ = sm;                    // [TT][dkp]
+    float* sK = sQ + TT * dkp;         // [TT][dkp]
+    float* sD = sK + TT * dkp;         // [TT][dkp] decay per key channel
+    float* sV = sD + TT * dkp;         // [TT][32]
+    float* sR = sV + TT * 32;          // [2][KS][32]
+    const int g = MODE == SCAN_SSD ? h / (a.heads / a.groups) : h;
+    const bool col_ok = j < dv;
+    float S[KPT], bon[KPT];
+    float* st = a.state + (((size_t)sg.slot * a.heads + h) * dk) * dv;
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+        const int key = ks * KPT + i;
+        S[i] = (sg.pos0 > 0 && col_ok && key < dk) ? st[(size_t)key * dv + j] : 0.f;
+        bon[i] = (MODE == SCAN_RWKV && key < dk) ? a.bonus[(size_t)h * dk + key] : 0.f;
+    }
+    float neg_a = 0.f, dtb = 0.f, skip = 0.f;
+    if (MODE == SCAN_SSD) { neg_a = -expf(a.a_log[h]); dtb = a.dt_bias[h]; skip = a.skip[h]; }
+
+    for (int t0 = 0; t0 < sg.n; t0 += TT) {
+        const int nt = min(TT, sg.n - t0);
+        __syncthreads();
+        for (int e = tid; e < nt * dkp; e += nthr) {
+            const int t = e / dkp, key = e % dkp;
+            const size_t row = (size_t)(sg.row0 + t0 + t);
+            float q = 0.f, k = 0.f, d = 1.f;
+            if (key < dk) {
+                q = a.q[row * a.ldq + (size_t)g * dk + key];
+                k = a.k[row * a.ldk + (size_t)g * dk + key];
+                if (MODE == SCAN_SSD) {
+                    const float dt = softplus_f(a.decay_in[row * a.ldd + h] + dtb);
+                    d = expf(neg_a * dt);
+                    k *= dt;
+                } else {
+                    d = expf(-expf(a.decay_in[row * a.ldd + (size_t)h * dk + key]));
+                }
+            }
+            sQ[e] = q; sK[e] = k; sD[e] = d;
+        }
+        for (int e = tid; e < nt * 32; e += nthr) {
+            const int t = e >> 5, jj = blockIdx.x * 32 + (e & 31);
+            sV[e] = jj < dv ? a.v[(size_t)(sg.row0 + t0 + t) * a.ldv + (size_t)h * dv + jj] : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float v = sV[t * 32 + threadIdx.x];
+            const float* q = sQ + t * dkp + ks * KPT;
+            const float* k = sK + t * dkp + ks * KPT;
+            const float* d = sD + t * dkp + ks * KPT;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < KPT; ++i) {
+                const float kv = k[i] * v;
+                if (MODE == SCAN_RWKV) {
+                    acc = fmaf(q[i], fmaf(bon[i], kv, S[i]), acc);
+                    S[i] = fmaf(d[i], S[i], kv);
+                } else {
+                    S[i] = fmaf(d[i], S[i], kv);
+                    acc = fmaf(q[i], S[i], acc);
+                }
+            }
+            float* red = sR + ((t0 + t) & 1) * KS * 32;
+            if (KS > 1) {
+                red[ks * 32 + threadIdx.x] = acc;
+                __syncthreads();
+                if (ks == 0) {
+                    acc = 0.f;
+                    for (int s = 0; s < KS; ++s) acc += red[s * 32 + threadIdx.x];
+                }
+            }
+            if (ks == 0 && col_ok) {
+                if (MODE == SCAN_SSD) acc = fmaf(skip, v, acc);
+                a.y[(size_t)(sg.row0 + t0 + t) * a.ldy + (size_t)h * dv + j] = acc;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < KPT; ++i) {
+        const int key = ks * KPT + i;
+        if (col_ok && key < dk) st[(size_t)key * dv + j] = S[i];
+    }
+}
+}  // namespace
+
+int causal_conv_silu_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C,
+                         int taps, const SeqSeg* segs, int nseg, cudaStream_t st) {
+    B2_CHECK_ARG(in && w && bias && tail && out && segs && C > 0 && nseg > 0, "causal_conv: bad argument");
+    B2_CHECK_ARG(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: 1..%d taps are supported (got %d)", CONV_MAX_TAPS, taps);
+    causal_conv_silu_kernel<<<dim3((C + 127) / 128, nseg), 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out, int64_t out_stride, int cols, int n_mix, const SeqSeg* segs,
+                        int nseg, cudaStream_t st) {
+    B2_CHECK_ARG(x && mu && prev && out && segs && cols > 0 && nseg > 0, "token_shift: bad argument");
+    B2_CHECK_ARG(n_mix >= 1 && n_mix <= SHIFT_MAX_MIX, "token_shift: 1..%d mixes are supported (got %d)", SHIFT_MAX_MIX, n_mix);
+    token_shift_mix_kernel<<<dim3((cols + 127) / 128, nseg), 128, 0, st>>>(x, mu, prev, out, out_stride, cols, n_mix, segs);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int linear_scan_f32(const ScanArgs& a, cudaStream_t st) {
+    B2_CHECK_ARG(a.q && a.k && a.v && a.decay_in && a.state && a.y && a.segs && a.nseg > 0, "linear_scan: null argument");
+    B2_CHECK_ARG(a.heads > 0 && a.dk > 0 && a.dv > 0, "linear_scan: bad sizes");
+    const int KS = (a.dk + KPT - 1) / KPT;
+    B2_CHECK_ARG(KS <= 16, "linear_scan: key size %d exceeds %d", a.dk, 16 * KPT);
+    const size_t smem = ((size_t)3 * TT * KS * KPT + TT * 32 + 2 * KS * 32) * sizeof(float);
+    dim3 grid((a.dv + 31) / 32, a.heads, a.nseg), block(32, KS);
+    if (a.mode == SCAN_SSD) {
+        B2_CHECK_ARG(a.groups > 0 && a.heads % a.groups == 0 && a.dt_bias && a.a_log && a.skip, "linear_scan(ssd): heads %d / groups %d", a.heads, a.groups);
+        if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_SSD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        linear_scan_kernel<SCAN_SSD><<<grid, block, smem, st>>>(a);
+    } else {
+        B2_CHECK_ARG(a.bonus != nullptr, "linear_scan(rwkv): null bonus");
+        if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_RWKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        linear_scan_kernel<SCAN_RWKV><<<grid, block, smem, st>>>(a);
+    }
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+}  // namespace b2

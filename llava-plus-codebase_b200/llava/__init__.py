@@ -14,4 +14,10 @@ if _ref:
     if _os.path.isdir(_p) and _p not in __path__:
         __path__.append(_p)  # our directory stays first: llava.model/* is ours, the rest falls through
 
-from .model import LlavaLlamaForCausalLM, LlavaConfig  # noqa: E402,F401
+
+
+def __getattr__(name):  # `from llava import LlavaLlamaForCausalLM` keeps working; nothing heavy is imported before it is asked for
+    if name in ("LlavaLlamaForCausalLM", "LlavaConfig", "KatadraForCausalLM", "KatadraConfig"):
+        from . import model
+        return getattr(model, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -53,6 +53,28 @@ class PreprocessPlan(_c.Structure):
                 ("pixels", _vp), ("u8_out", _vp)]
 
 
+class SeqLayerDesc(_c.Structure):
+    """b2_seq_layer_desc (include/b2llava.h): one entry of a layer-list decoder."""
+    _fields_ = [("type", _c.c_int32), ("weights_of", _c.c_int32), ("ff", _c.c_int32),
+                ("m_heads", _c.c_int32), ("m_vdim", _c.c_int32), ("m_state", _c.c_int32), ("m_groups", _c.c_int32),
+                ("m_conv", _c.c_int32), ("m_norm_groups", _c.c_int32),
+                ("a_heads", _c.c_int32), ("a_kv_heads", _c.c_int32), ("a_dim", _c.c_int32), ("a_vdim", _c.c_int32),
+                ("a_rel_rows", _c.c_int32), ("a_bias_max", _c.c_float), ("a_scale", _c.c_float), ("a_softcap", _c.c_float),
+                ("a_temp_coef", _c.c_float), ("a_temp_every", _c.c_float),
+                ("r_heads", _c.c_int32), ("r_dim", _c.c_int32), ("r_decay_rank", _c.c_int32),
+                ("left_scale", _c.c_float), ("right_scale", _c.c_float)]
+
+
+class SeqModelDesc(_c.Structure):
+    """b2_seq_model_desc (include/b2llava.h)."""
+    _fields_ = [("width", _c.c_int32), ("vocab", _c.c_int32), ("n_layers", _c.c_int32), ("compute", _c.c_int32),
+                ("norm_eps", _c.c_float), ("max_batch", _c.c_int32), ("max_rows", _c.c_int32)]
+
+
+MIXER_MAMBA2, MIXER_PARALLEL = 1, 2
+COMPUTE_BF16, COMPUTE_F32 = 0, 1
+
+
 def make_sampling(do_sample=False, temperature=1.0, top_p=1.0, top_k=0, seed=0):
     return Sampling(int(bool(do_sample)), float(temperature), float(1.0 if top_p is None else top_p),
                     int(top_k or 0), int(seed) & (2**64 - 1))
@@ -91,6 +113,11 @@ SIGNATURES = {
     "b2_decode_step": (_i32, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
     "b2_decode_greedy": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp]),
     "b2_argmax": (_i32, [_vp, _i32, _i32, _vp, _vp]),
+    "b2_seq_model_create": (_i32, [_c.POINTER(SeqModelDesc), _c.POINTER(SeqLayerDesc), _c.POINTER(_vp)]),
+    "b2_append_tokens": (_i32, [_vp, _vp, _i32, _c.POINTER(_c.c_int32), _i32, _i32, _c.POINTER(_c.c_int32), _i32, _vp, _vp, _vp]),
+    "b2_decode_step_slots": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp]),
+    "b2_kv_free_slot": (_i32, [_vp, _i32, _vp]),
+    "b2_kv_bytes": (_i64, [_vp, _i32, _i32]),
     "b2_op_gemm": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b2_op_gemv": (_i32, [_vp, _i64, _vp, _i32, _vp, _f32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b2_op_gemm_skinny": (_i32, [_vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp]),
@@ -196,6 +223,11 @@ class KVCache:
 
     def get_seq_length(self, layer_idx=0):
         return self.lengths(1)[0]
+
+    def free_slot(self, slot):
+        """Give a slot back (length 0); what it held is dead and needs no clearing."""
+        with torch.cuda.device(self.engine.index):
+            check(self.engine.lib.b2_kv_free_slot(self.handle, int(slot), stream_ptr()), "b2_kv_free_slot")
 
     def close(self):
         if getattr(self, "handle", None) is not None and self.handle.value:
@@ -421,3 +453,66 @@ class Engine:
             self.close()
         except Exception:
             pass
+
+
+class SeqEngine(Engine):
+    """Engine of a layer-list decoder (include/b2llava.h, "layer-list decoders"): same handle, caches, decode / streaming /
+    batching calls as the LLaVA engine; prompts come as token ids in portions (`append_tokens`)."""
+
+    def __init__(self, model_desc: dict, layer_descs, device):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("b2llava SeqEngine requires a CUDA device; there is no CPU path")
+        self.index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        self.lib = init(self.index)
+        self.desc = SeqModelDesc(n_layers=len(layer_descs), **model_desc)
+        self.layer_descs = (SeqLayerDesc * len(layer_descs))(*[SeqLayerDesc(**d) for d in layer_descs])
+        h = _vp()
+        with torch.cuda.device(self.index):
+            check(self.lib.b2_seq_model_create(ctypes.byref(self.desc), self.layer_descs, ctypes.byref(h)), "b2_seq_model_create")
+        self.handle = h
+        self.hidden, self.vocab = model_desc["width"], model_desc["vocab"]
+        self.finalized = False
+        self._kvs = weakref.WeakSet()
+
+    def kv_bytes(self, max_batch, max_seq):
+        return int(self.lib.b2_kv_bytes(self.handle, int(max_batch), int(max_seq)))
+
+    def append_tokens(self, kv, slot, tokens, want=(), restart=False, residuals=False):
+        """Feed the next tokens of the request in `slot`; returns fp32 logits [len(want), vocab] on the device for the
+        positions `want` (indices into `tokens`), and with residuals=True also the residual stream after every layer
+        [layers, n, width]."""
+        toks = [int(t) for t in tokens]
+        n, nw = len(toks), len(want)
+        ctoks = (_c.c_int32 * n)(*toks)
+        cwant = (_c.c_int32 * max(nw, 1))(*[int(w) for w in want])
+        logits = torch.empty(nw, self.vocab, dtype=torch.float32, device=self.device) if nw else None
+        resid = torch.empty(self.desc.n_layers, n, self.hidden, dtype=torch.float32, device=self.device) if residuals else None
+        with torch.cuda.device(self.index):
+            check(self.lib.b2_append_tokens(self.handle, kv.handle, int(slot), ctoks, n, int(bool(restart)), cwant, nw, ptr(logits),
+                                            ptr(resid), stream_ptr()), "b2_append_tokens")
+        return (logits, resid) if residuals else logits
+
+    def prefill(self, kv, tokens, seq_lens=None, logits_mode=LOGITS_LAST, slot0=0):
+        """Engine.prefill for token ids [B, S] (right-padded rows with seq_lens valid tokens): every row restarts its slot."""
+        ids = tokens.reshape(-1, tokens.shape[-1]).tolist() if torch.is_tensor(tokens) else [list(r) for r in tokens]
+        out = []
+        for b, row in enumerate(ids):
+            n = int(seq_lens[b]) if seq_lens is not None else len(row)
+            want = [] if logits_mode == LOGITS_NONE else ([n - 1] if logits_mode == LOGITS_LAST else list(range(n)))
+            lg = self.append_tokens(kv, slot0 + b, row[:n], want, restart=True)
+            if logits_mode == LOGITS_ALL and n < len(row):
+                lg = torch.cat([lg, lg.new_zeros(len(row) - n, self.vocab)])
+            out.append(lg)
+        if logits_mode == LOGITS_NONE:
+            return None
+        return torch.cat(out) if logits_mode == LOGITS_LAST else torch.stack(out)
+
+    def decode_step(self, kv, tokens, want_logits=True, slot0=0):
+        tokens = tokens.to(torch.int32).contiguous()
+        B = tokens.numel()
+        logits = torch.empty(B, self.vocab, dtype=torch.float32, device=self.device) if want_logits else None
+        with torch.cuda.device(self.index):
+            check(self.lib.b2_decode_step_slots(self.handle, kv.handle, ptr(tokens), B, int(slot0), ptr(logits), _vp(0), stream_ptr()),
+                  "b2_decode_step")
+        return logits

@@ -1,5 +1,34 @@
-"""`llava.model` on the B200 engine: the LLaMA/Vicuna LLaVA classes only (the reference also exports an MPT
-variant, llava/model/__init__.py:2, which is outside the north-star path)."""
-from .language_model.llava_llama import LlavaConfig, LlavaLlamaForCausalLM
+"""`llava.model` on the B200 engine: the LLaMA/Vicuna LLaVA classes (the reference also exports an MPT variant,
+llava/model/__init__.py:2, which is outside the north-star path) and the registry of every model family this package
+serves, keyed by what a checkpoint's config.json calls itself (`model_type` of HF-style configurations, `architecture` of
+layer-list decoders). Classes are imported on first use: a text-only model does not pay for the multimodal imports."""
+import importlib
+import json
+import os
 
-__all__ = ["LlavaConfig", "LlavaLlamaForCausalLM"]
+# name in config.json -> (module under llava.model, class)
+MODEL_REGISTRY = {
+    "llava": ("language_model.llava_llama", "LlavaLlamaForCausalLM"),
+    "Katadra": ("language_model.katadra", "KatadraForCausalLM"),
+}
+_LAZY = {"LlavaLlamaForCausalLM": "language_model.llava_llama", "LlavaConfig": "language_model.llava_llama",
+         "KatadraForCausalLM": "language_model.katadra", "KatadraConfig": "language_model.katadra"}
+
+__all__ = ["LlavaConfig", "LlavaLlamaForCausalLM", "KatadraConfig", "KatadraForCausalLM", "MODEL_REGISTRY", "model_class_for"]
+
+
+def __getattr__(name):
+    if name in _LAZY:
+        return getattr(importlib.import_module("." + _LAZY[name], __name__), name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
+def model_class_for(model_path):
+    """The class that serves the checkpoint directory `model_path`, chosen by its config.json."""
+    with open(os.path.join(model_path, "config.json")) as f:
+        cfg = json.load(f)
+    name = cfg.get("architecture") or cfg.get("model_type")
+    if name not in MODEL_REGISTRY:
+        raise NotImplementedError(f"{model_path}: no model of this package serves {name!r} (known: {sorted(MODEL_REGISTRY)})")
+    mod, cls = MODEL_REGISTRY[name]
+    return getattr(importlib.import_module("." + mod, __name__), cls)

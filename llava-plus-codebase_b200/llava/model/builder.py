@@ -3,12 +3,12 @@
 (LLaMA/Vicuna) checkpoints from a local directory. LoRA merging, MPT, projector-only checkpoints on a base LLM
 and bitsandbytes 8/4-bit loading are checkpoint surgery outside the hot path and raise NotImplementedError.
 """
+import json
 import os
 
 import torch
-from transformers import AutoTokenizer
 
-from .language_model.llava_llama import LlavaLlamaForCausalLM
+from . import MODEL_REGISTRY, model_class_for
 from ..constants import DEFAULT_IMAGE_PATCH_TOKEN, DEFAULT_IM_START_TOKEN, DEFAULT_IM_END_TOKEN
 
 
@@ -16,12 +16,23 @@ def load_pretrained_model(model_path, model_base, model_name, load_8bit=False, l
                           device="cuda"):
     if load_8bit or load_4bit:
         raise NotImplementedError("bitsandbytes 8/4-bit loading is not part of the B200 path (bf16 weights)")
+    cfg_file = os.path.join(model_path, "config.json")
+    if os.path.isfile(cfg_file):
+        with open(cfg_file) as f:
+            arch = json.load(f).get("architecture")
+        if arch in MODEL_REGISTRY and arch != "llava":
+            # a text-only layer-list decoder: no tokenizer or image processor ships with it; the caller feeds token ids
+            model = model_class_for(model_path).from_pretrained(model_path, device=device)
+            return None, model, None, model._limits["max_seq"]
     if "llava" not in model_name.lower():
         raise NotImplementedError("only LLaVA (LLaMA/Vicuna) checkpoints are served by this package")
     if "lora" in model_name.lower() or model_base is not None or "mpt" in model_name.lower():
         raise NotImplementedError("LoRA / delta / MPT checkpoints: merge offline with the reference's scripts first")
     if device != "cuda" and not str(device).startswith("cuda"):
         raise RuntimeError("the B200 path needs a CUDA (sm_100a) device; there is no CPU fallback")
+
+    from transformers import AutoTokenizer
+    from .language_model.llava_llama import LlavaLlamaForCausalLM
 
     tokenizer = AutoTokenizer.from_pretrained(model_path, use_fast=False)
     model = LlavaLlamaForCausalLM.from_pretrained(model_path, low_cpu_mem_usage=True, device=device)
