@@ -54,6 +54,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the side measurements of the other BASELINE configs")
+    ap.add_argument("--arch", default="llava", choices=["llava", "katadra"],
+                    help="katadra: prefill / decode throughput of the layer-list decoder beside the LLaMA decoder of equal width, "
+                         "depth and parameter count (random weights); the default workload and its JSON line are unchanged")
+    ap.add_argument("--widths", default="2048,4096", help="--arch katadra: model widths to measure")
+    ap.add_argument("--ctx", type=int, default=2048, help="--arch katadra: prompt length")
     return ap.parse_args()
 
 
@@ -733,8 +738,121 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --arch katadra: the layer-list decoder beside the LLaMA decoder at equal size
+# ---------------------------------------------------------------------------------------------------------
+def katadra_config(width, layers, ctx):
+    """[mamba2, parallel] pairs: one pair holds about the parameters of two LLaMA layers of the same width."""
+    mamba = {"type": "mamba2", "mlp": None,
+             "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    heads = width // 128
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": 4 * width},
+           "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "bias_max": ctx, "scale": 128 ** -0.5,
+                              "softcap": 30.0, "q_temp": {"coef": 0.5, "every": 256}, "rel_rows": 32},
+                     "right": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "left_scale": 1.0, "right_scale": 1.0}}
+    return {"architecture": "Katadra", "width": width, "vocab": 32000, "norm": {"eps": 1e-5}, "layers": [mamba, par] * (layers // 2)}
+
+
+def timed(fn, steps, warmup, flush):
+    """median ms of fn() over `steps` runs after `warmup`, CUDA events on the current stream, L2 flushed before every run"""
+    ts = []
+    for i in range(warmup + steps):
+        flush.add_(1.0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def run_katadra(args):
+    from oracle import katadra_oracle as KO
+    from llava.model import KatadraConfig, KatadraForCausalLM
+    from llava._b2 import LOGITS_LAST, launch_count
+
+    dev = torch.device("cuda:0")
+    pk = peaks()
+    S, N, layers = args.ctx, 64, 4
+    flush = torch.zeros(160 * 1024 * 1024 // 4, device=dev)  # 160 MB > 126 MB of L2
+    out = {"metric": "layer-list decoder vs LLaMA decoder at equal size", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+           "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "source": pk["source"]}, "prompt": S, "decode_steps": N,
+           "l2": "160 MB written before every timed run", "sizes": []}
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    for width in [int(w) for w in args.widths.split(",")]:
+        row = {"width": width, "layers": layers}
+        # ---- Katadra --------------------------------------------------------------------------------------------------
+        cfg = katadra_config(width, layers, S + N + 8)
+        w = KO.random_weights(cfg, seed=0)
+        params = sum(v.numel() for k, v in w.items() if v.dim() == 2 and k != "embed")
+        model = KatadraForCausalLM(KatadraConfig(**cfg), {k: v.bfloat16() for k, v in w.items()}, device=dev, dtype=torch.bfloat16,
+                                   max_batch=8, max_seq=S + N + 8, max_rows=S)
+        del w
+        eng = model._ensure_engine()
+        kv = eng.new_kv(8, S + N + 8)
+        toks = torch.randint(0, 32000, (S,)).tolist()
+        t_pre = timed(lambda: eng.append_tokens(kv, 0, toks, [S - 1], restart=True), args.steps, args.warmup, flush)
+        res = {"params_matmul": params, "prefill_ms": round(t_pre, 3), "prefill_tok_s": round(S / t_pre * 1e3, 1),
+               "prefill_frac_bf16_peak": round(2.0 * params * S / (t_pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               "state_bytes_per_slot": eng.kv_bytes(1, S)}
+        for B in (1, 8):
+            for b in range(B):
+                eng.append_tokens(kv, b, toks, [], restart=True)
+            first = torch.zeros(B, dtype=torch.int32, device=dev)
+            eng.decode_greedy(kv, first, 4)                                   # eager step + graph capture
+            for b in range(B):
+                eng.append_tokens(kv, b, toks, [], restart=True)
+            t = timed(lambda: eng.decode_greedy(kv, first, N), 1, 0, flush) / N
+            moved = 2.0 * params + B * eng.kv_bytes(1, S)                      # weights once + every slot's state and key/value rows
+            res[f"decode_b{B}_ms_per_step"] = round(t, 4)
+            res[f"decode_b{B}_tok_s"] = round(B / t * 1e3, 1)
+            res[f"decode_b{B}_frac_hbm_peak"] = round(moved / (t * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
+        row["katadra"] = res
+        model.invalidate_engine()
+        del model, eng, kv
+        # ---- LLaMA decoder of the same width and depth ------------------------------------------------------------------------
+        m = {"name": f"llama-w{width}", "hidden": width, "inter": (int(width * 8 / 3) + 255) // 256 * 256, "layers": layers, "heads": width // 128}
+        lm = build_model(m, dev, 8, S + N + 8)
+        le = lm._ensure_engine()
+        lparams = layers * (4 * width * width + 3 * width * m["inter"]) + 32000 * width
+        lkv = le.new_kv(8, S + N + 8)
+        emb = torch.randn(1, S, width, device=dev, dtype=torch.bfloat16)
+        t_pre = timed(lambda: le.prefill(lkv, emb, [S], LOGITS_LAST), args.steps, args.warmup, flush)
+        res = {"params_matmul": lparams, "prefill_ms": round(t_pre, 3), "prefill_tok_s": round(S / t_pre * 1e3, 1),
+               "prefill_frac_bf16_peak": round(2.0 * lparams * S / (t_pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        for B in (1, 8):
+            embB = emb.expand(B, S, width).contiguous()
+            le.prefill(lkv, embB, [S] * B, LOGITS_LAST)
+            first = torch.zeros(B, dtype=torch.int32, device=dev)
+            le.decode_greedy(lkv, first, 4)
+            lkv.reset()
+            le.prefill(lkv, embB, [S] * B, LOGITS_LAST)
+            t = timed(lambda: le.decode_greedy(lkv, first, N), 1, 0, flush) / N
+            moved = 2.0 * lparams + B * 2.0 * layers * S * width * 2
+            res[f"decode_b{B}_ms_per_step"] = round(t, 4)
+            res[f"decode_b{B}_tok_s"] = round(B / t * 1e3, 1)
+            res[f"decode_b{B}_frac_hbm_peak"] = round(moved / (t * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
+        row["llama"] = res
+        lm.invalidate_engine()
+        del lm, le, lkv
+        out["sizes"].append(row)
+    out["clocks"] = sampler.stop()
+    out["gpu_launches"] = launch_count() - launches0
+    print(json.dumps(out))
+
+
 def main():
     args = parse_args()
+    if args.arch == "katadra":
+        if not torch.cuda.is_available():
+            raise RuntimeError("bench.py --arch katadra needs a B200")
+        return run_katadra(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -59,6 +59,28 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 bool pdl_enabled();  // B2_PDL=0 turns the launch attribute off (A/B runs)
 
+// ----------------------------------------------------------------------------------------------
+// Extras of the GEMMs' fp32-output epilogue (layer-list decoders): an activation chosen at run time, a scale, and
+// accumulation onto what the output already holds. Codes match LIN_* in kernels.h.
+// ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ float epi_post_act(float v, int post) {
+    switch (post) {
+        case 1: return v / (1.f + expf(-v));        // SiLU
+        case 2: return 1.f / (1.f + expf(-v));      // sigmoid
+        case 3: return tanhf(v);
+        case 4: { const float r = v > 0.f ? v : 0.f; return r * r; }  // relu^2
+        default: return v;
+    }
+}
+__device__ __forceinline__ void epi_post8(float (&x)[8], const float* op, int post, float alpha, int accumulate) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = alpha * epi_post_act(x[e], post);
+    if (accumulate) {
+        const float4 a = *reinterpret_cast<const float4*>(op), b = *reinterpret_cast<const float4*>(op + 4);
+        x[0] += a.x; x[1] += a.y; x[2] += a.z; x[3] += a.w; x[4] += b.x; x[5] += b.y; x[6] += b.z; x[7] += b.w;
+    }
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};

@@ -48,6 +48,9 @@ struct PairEpi {
     const __nv_bfloat16* residual;
     void* out;
     int ld_out, ld_res, out_fp32;
+    int post = 0;          // fp32 output only: LIN_* activation, scale, accumulate onto the output
+    float alpha = 1.f;
+    int accumulate = 0;
     // ACT_ROPE_QKV
     const uint32_t* rope_tab;
     __nv_bfloat16* kcache;
@@ -338,6 +341,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                         }
                         if (ep.out_fp32) {
                             float* op = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ld_out + col;
+                            if (ep.post != 0 || ep.accumulate != 0 || ep.alpha != 1.f) epi_post8(x, op, ep.post, ep.alpha, ep.accumulate);
                             *reinterpret_cast<float4*>(op) = make_float4(x[0], x[1], x[2], x[3]);
                             *reinterpret_cast<float4*>(op + 4) = make_float4(x[4], x[5], x[6], x[7]);
                         } else {
@@ -398,6 +402,7 @@ int gemm_bf16_2cta(const GemmArgs& g, cudaStream_t stream) {
     ep.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
     ep.residual = reinterpret_cast<const __nv_bfloat16*>(g.residual);
     ep.out = g.out; ep.ld_out = g.ld_out; ep.ld_res = g.ld_res; ep.out_fp32 = g.out_fp32;
+    ep.post = g.out_fp32 ? g.post : 0; ep.alpha = g.out_fp32 ? g.alpha : 1.f; ep.accumulate = g.out_fp32 ? g.accumulate : 0;
     ep.rope_tab = reinterpret_cast<const uint32_t*>(g.rope.table);
     ep.kcache = reinterpret_cast<__nv_bfloat16*>(g.rope.kcache); ep.vcache = reinterpret_cast<__nv_bfloat16*>(g.rope.vcache);
     ep.rope_S = g.rope.S; ep.rope_H = g.rope.H; ep.rope_Smax = g.rope.Smax;

@@ -124,6 +124,9 @@ struct EpiParams {
     int ld_out;
     int ld_res;
     int out_fp32;
+    int post = 0;          // fp32 output only: LIN_* activation, scale, accumulate onto the output
+    float alpha = 1.f;
+    int accumulate = 0;
 };
 
 __device__ __forceinline__ float act_quick_gelu(float x) { return __fdividef(x, 1.0f + __expf(-1.702f * x)); }
@@ -350,6 +353,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         }
                         if (ep.out_fp32) {
                             float* op = reinterpret_cast<float*>(ep.out) + (size_t)row * ep.ld_out + col;
+                            if (ep.post != 0 || ep.accumulate != 0 || ep.alpha != 1.f) epi_post8(x, op, ep.post, ep.alpha, ep.accumulate);
                             *reinterpret_cast<float4*>(op) = make_float4(x[0], x[1], x[2], x[3]);
                             *reinterpret_cast<float4*>(op + 4) = make_float4(x[4], x[5], x[6], x[7]);
                         } else {
@@ -708,6 +712,7 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
     ep.ld_out = g.ld_out;
     ep.ld_res = g.ld_res;
     ep.out_fp32 = g.out_fp32;
+    ep.post = g.out_fp32 ? g.post : 0; ep.alpha = g.out_fp32 ? g.alpha : 1.f; ep.accumulate = g.out_fp32 ? g.accumulate : 0;
 
     if (g.act == ACT_SWIGLU) {
         if (bn == 256) return launch_gemm<256, ACT_SWIGLU>(ta, tb, g.M, g.N, g.K, ep, stream);

@@ -35,6 +35,8 @@ struct GemmArgs {
     int act = ACT_NONE;
     int bn_override = 0;  // 0 = cost-model heuristic, else 64/128/192/256 (2 = CTA-pair kernel)
     RopeQkv rope;         // ACT_ROPE_QKV only
+    // fp32 output only (layer-list decoders): out = alpha * post(acc + bias + residual) (+ out when accumulate); post = LIN_*
+    int post = 0; float alpha = 1.f; int accumulate = 0;
 };
 int gemm_bf16(const GemmArgs& g, cudaStream_t stream);
 // mm_projector mlp2x_gelu as ONE kernel (gemm_tcgen05.cu, projector_fused_kernel): out = gelu_erf(X W1^T + b1) W2^T + b2.
@@ -281,6 +283,8 @@ struct LinearArgs {
     int round_a = 0;                             // round A to bf16 first (bf16 compute: the product is bf16 x bf16 -> fp32)
 };
 int linear_f32(const LinearArgs& a, cudaStream_t stream);
+// out[r, :K] = bf16(A[r, :K]): the A operand of a tensor-core GEMM from fp32 activations (ld_out % 8 == 0)
+int cast_rows_bf16(const float* A, int64_t lda, void* out, int64_t ld_out, int M, int K, cudaStream_t stream);
 
 // ---- fp32 norms and row helpers (norms_f32.cu) ------------------------------------------------------------------------
 // x[r] += LayerNorm(y[r]) * gamma + beta   (normalisation of a sublayer's OUTPUT, added to the residual stream)

@@ -27,18 +27,20 @@ __device__ __forceinline__ void lin_store(float* o, float acc, const float* bias
     *o = accumulate ? (*o + v) : v;
 }
 
-__device__ __forceinline__ void ld_w4(const float* p, float (&w)[4]) {
-    const float4 t = *reinterpret_cast<const float4*>(p);
-    w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+// ---- up to MR rows: one warp per output column, the weight row is read exactly once --------------------------------------
+// VEC: a lane takes 8 consecutive k per step (16 B of bf16 weights, 2 x 16 B of fp32), two steps in flight.
+constexpr int MR = 8;
+__device__ __forceinline__ void ld_w8(const float* p, float (&w)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
 }
-__device__ __forceinline__ void ld_w4(const __nv_bfloat16* p, float (&w)[4]) {
-    const uint2 t = *reinterpret_cast<const uint2*>(p);
+__device__ __forceinline__ void ld_w8(const __nv_bfloat16* p, float (&w)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
     w[0] = __uint_as_float(t.x << 16); w[1] = __uint_as_float(t.x & 0xffff0000u);
     w[2] = __uint_as_float(t.y << 16); w[3] = __uint_as_float(t.y & 0xffff0000u);
+    w[4] = __uint_as_float(t.z << 16); w[5] = __uint_as_float(t.z & 0xffff0000u);
+    w[6] = __uint_as_float(t.w << 16); w[7] = __uint_as_float(t.w & 0xffff0000u);
 }
-
-// ---- up to MR rows: one warp per output column, the weight row is read exactly once --------------------------------------
-constexpr int MR = 8;
 template <typename TW, bool VEC>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const float* __restrict__ A, int64_t lda, const TW* __restrict__ W, int64_t ldw,
                                                           const float* __restrict__ bias, float* __restrict__ out, int64_t ld_out, int M, int N,
@@ -51,16 +53,24 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const float* __restric
 #pragma unroll
     for (int m = 0; m < MR; ++m) acc[m] = 0.f;
     if (VEC) {
-        for (int k = lane * 4; k < K; k += 128) {
-            float wv[4];
-            ld_w4(w + k, wv);
+        for (int k0 = lane * 8; k0 < K; k0 += 512) {
+            float wv[2][8];
+            const int k1 = k0 + 256;
+            ld_w8(w + k0, wv[0]);
+            if (k1 < K) ld_w8(w + k1, wv[1]);
 #pragma unroll
-            for (int m = 0; m < MR; ++m) {
-                if (m < M) {
-                    float4 a = *reinterpret_cast<const float4*>(A + (size_t)m * lda + k);
-                    if (round_a) { a.x = round_bf16(a.x); a.y = round_bf16(a.y); a.z = round_bf16(a.z); a.w = round_bf16(a.w); }
-                    acc[m] = fmaf(a.x, wv[0], acc[m]); acc[m] = fmaf(a.y, wv[1], acc[m]);
-                    acc[m] = fmaf(a.z, wv[2], acc[m]); acc[m] = fmaf(a.w, wv[3], acc[m]);
+            for (int u = 0; u < 2; ++u) {
+                const int k = u == 0 ? k0 : k1;
+                if (k < K) {
+#pragma unroll
+                    for (int m = 0; m < MR; ++m) {
+                        if (m < M) {
+                            float av[8];
+                            ld_w8(A + (size_t)m * lda + k, av);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[m] = fmaf(round_a ? round_bf16(av[e]) : av[e], wv[u][e], acc[m]);
+                        }
+                    }
                 }
             }
         }
@@ -145,7 +155,7 @@ template <typename TW>
 int launch_linear(const LinearArgs& a, cudaStream_t st) {
     const TW* W = reinterpret_cast<const TW*>(a.W);
     if (a.M <= MR) {
-        const bool vec = a.K % 4 == 0 && a.lda % 4 == 0 && a.ldw % 4 == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0 &&
+        const bool vec = a.K % 8 == 0 && a.lda % 4 == 0 && a.ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(a.W) & 15) == 0;
         dim3 grid((a.N + 7) / 8);
         if (vec)
@@ -163,6 +173,25 @@ int launch_linear(const LinearArgs& a, cudaStream_t st) {
     return 0;
 }
 }  // namespace
+
+namespace {
+__global__ void cast_rows_bf16_kernel(const float* __restrict__ A, int64_t lda, __nv_bfloat16* __restrict__ out, int64_t ld_out, int K) {
+    const size_t r = blockIdx.y;
+    const int k = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (k + 1 < K) {
+        *reinterpret_cast<__nv_bfloat162*>(out + r * ld_out + k) = __floats2bfloat162_rn(A[r * lda + k], A[r * lda + k + 1]);
+    } else if (k < K) {
+        out[r * ld_out + k] = __float2bfloat16_rn(A[r * lda + k]);
+    }
+}
+}  // namespace
+
+int cast_rows_bf16(const float* A, int64_t lda, void* out, int64_t ld_out, int M, int K, cudaStream_t st) {
+    B2_CHECK_ARG(A && out && M > 0 && K > 0 && ld_out % 2 == 0, "cast_rows_bf16: bad argument");
+    cast_rows_bf16_kernel<<<dim3((K / 2 + 256) / 256, M), 256, 0, st>>>(A, lda, reinterpret_cast<__nv_bfloat16*>(out), ld_out, K);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
 
 int linear_f32(const LinearArgs& a, cudaStream_t st) {
     B2_CHECK_ARG(a.A && a.W && a.out && a.M > 0 && a.N > 0 && a.K > 0, "linear: bad argument (M=%d N=%d K=%d)", a.M, a.N, a.K);

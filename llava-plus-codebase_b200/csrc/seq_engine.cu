@@ -30,6 +30,7 @@ struct SeqLayerInfo {
     int inner = 0, conv_ch = 0, dproj = 0;            // mamba2: heads*vdim, inner + 2*groups*state, 2*inner + 2*groups*state + heads
     int nq = 0, nk = 0, nv = 0, ng = 0, lproj = 0;    // attention projection widths
     int rn = 0;                                       // RWKV heads*dim
+    int dproj_ld = 0, lproj_ld = 0;                   // row pitch of the projection outputs (multiples of 8: tensor-core epilogue)
 };
 
 struct SeqModel {
@@ -42,6 +43,8 @@ struct SeqModel {
     int rows = 0;                      // workspace rows
     // workspaces (fp32 unless noted)
     DevBuf x, proj, act, y, gated, mixout, mixes, rp, wl1, wlog, ff, xn, tok, want;
+    DevBuf a16;                        // bf16 copy of a GEMM's A operand (tensor-core path of the bf16 compute mode)
+    int a16_w = 0;
     DevBuf segs, row_slot, row_pos;
     int proj_w = 0, act_w = 0, y_w = 0, rp_w = 0, rank_w = 0, ff_w = 0;
 };
@@ -71,7 +74,10 @@ int64_t numel(const int64_t* shape, int ndim) {
 // host-or-device tensor of `dtype` -> device buffer of `to` (DT_F32 or DT_BF16), at element offset `off` of a buffer of
 // `total` elements (allocated on first use)
 int put_tensor(DevBuf& buf, int to, size_t total, size_t off, const void* src, int dtype, int64_t n) {
-    if (buf.p == nullptr) B2_TRY(buf.alloc(total * esz(to)));
+    if (buf.p == nullptr) {
+        B2_TRY(buf.alloc(total * esz(to)));
+        B2_CUDA_CHECK(cudaMemset(buf.p, 0, total * esz(to)));
+    }
     cudaPointerAttributes attr;
     bool on_device = false;
     if (cudaPointerGetAttributes(&attr, src) == cudaSuccess) on_device = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
@@ -106,6 +112,11 @@ int want_shape(const char* key, const int64_t* shape, int ndim, int64_t a, int64
     return 0;
 }
 
+bool tc_enabled() {  // B2_SEQ_TC=0: every Linear on the FMA kernels (A/B runs, tests of the two paths against each other)
+    const char* e = getenv("B2_SEQ_TC");
+    return !(e != nullptr && e[0] == '0');
+}
+
 struct Lin {  // one Linear call on the model's compute dtype
     const b2_model* m;
     cudaStream_t st;
@@ -117,6 +128,17 @@ struct Lin {  // one Linear call on the model's compute dtype
         a.W = reinterpret_cast<const char*>(W.p) + w_row0 * (size_t)K * esz(s.w_dtype);
         a.bias = bias; a.out = out; a.ld_out = ldo; a.M = M; a.N = N; a.K = K; a.act = act; a.alpha = alpha; a.accumulate = accumulate;
         a.round_a = s.d.compute == B2_COMPUTE_BF16;
+        // bf16 compute, a portion of a prompt: the tcgen05 GEMM on a bf16 copy of A (weights are stored with their rows
+        // padded to a multiple of 8, zero-filled, so N rounds up; the pitch of every projection buffer is a multiple of 8)
+        const int Np = (N + 7) / 8 * 8;
+        if (a.round_a && M >= 32 && N >= 32 && K % 8 == 0 && K >= 32 && K <= s.a16_w && ldo % 8 == 0 && Np <= ldo && bias == nullptr &&
+            w_row0 == 0 && tc_enabled()) {
+            B2_TRY(cast_rows_bf16(A, lda, s.a16.p, K, M, K, st));
+            GemmArgs g;
+            g.A = s.a16.p; g.lda = K; g.W = W.p; g.ldw = K; g.out = out; g.ld_out = (int)ldo; g.out_fp32 = 1;
+            g.M = M; g.N = Np; g.K = K; g.act = ACT_NONE; g.post = act; g.alpha = alpha; g.accumulate = accumulate;
+            return gemm_bf16(g, st);
+        }
         return linear_f32(a, st);
     }
 };
@@ -153,33 +175,33 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
         if (d.type == B2_MIXER_MAMBA2) {
             float* proj = s.proj.as<float>();
             const int gn = d.m_groups * d.m_state;
-            B2_TRY(lin(x, width, W.in_w, L.dproj, width, proj, L.dproj, R));
+            B2_TRY(lin(x, width, W.in_w, L.dproj, width, proj, L.dproj_ld, R));
             float* act = s.act.as<float>();  // [R, conv_ch] = silu(conv(x | B | C))
-            B2_TRY(causal_conv_silu_f32(proj + L.inner, L.dproj, W.conv_w.as<float>(), W.conv_b.as<float>(), S.conv_tail.as<float>(), act,
+            B2_TRY(causal_conv_silu_f32(proj + L.inner, L.dproj_ld, W.conv_w.as<float>(), W.conv_b.as<float>(), S.conv_tail.as<float>(), act,
                                         L.conv_ch, L.conv_ch, d.m_conv, segs, nseg, st));
             ScanArgs sa;
             sa.mode = SCAN_SSD;
             sa.v = act; sa.ldv = L.conv_ch;
             sa.k = act + L.inner; sa.ldk = L.conv_ch;
             sa.q = act + L.inner + gn; sa.ldq = L.conv_ch;
-            sa.decay_in = proj + 2 * L.inner + 2 * gn; sa.ldd = L.dproj;
+            sa.decay_in = proj + 2 * L.inner + 2 * gn; sa.ldd = L.dproj_ld;
             sa.dt_bias = W.dt_bias.as<float>(); sa.a_log = W.a_log.as<float>(); sa.skip = W.skip.as<float>();
             sa.state = S.ssm.as<float>();
             sa.y = s.y.as<float>(); sa.ldy = L.inner;
             sa.heads = d.m_heads; sa.groups = d.m_groups; sa.dk = d.m_state; sa.dv = d.m_vdim;
             sa.segs = segs; sa.nseg = nseg;
             B2_TRY(linear_scan_f32(sa, st));
-            B2_TRY(gated_group_rmsnorm_f32(s.y.as<float>(), L.inner, proj, L.dproj, W.mnorm.as<float>(), s.gated.as<float>(), L.inner, R, L.inner,
+            B2_TRY(gated_group_rmsnorm_f32(s.y.as<float>(), L.inner, proj, L.dproj_ld, W.mnorm.as<float>(), s.gated.as<float>(), L.inner, R, L.inner,
                                            L.inner / d.m_norm_groups, 1, eps, st));
             B2_TRY(lin(s.gated.as<float>(), L.inner, W.o_w, width, L.inner, mix, width, R));
         } else {
             // ---- left: attention -------------------------------------------------------------------------------------
             float* proj = s.proj.as<float>();  // [R, nq | nk | nv | ng]
-            B2_TRY(lin(x, width, W.lproj_w, L.lproj, width, proj, L.lproj, R));
+            B2_TRY(lin(x, width, W.lproj_w, L.lproj, width, proj, L.lproj_ld, R));
             BiasAttnArgs aa;
-            aa.q = proj; aa.ldq = L.lproj;
-            aa.k = proj + L.nq; aa.ldk = L.lproj;
-            aa.v = proj + L.nq + L.nk; aa.ldv = L.lproj;
+            aa.q = proj; aa.ldq = L.lproj_ld;
+            aa.k = proj + L.nq; aa.ldk = L.lproj_ld;
+            aa.v = proj + L.nq + L.nk; aa.ldv = L.lproj_ld;
             aa.kcache = S.kc.as<float>(); aa.vcache = S.vc.as<float>();
             aa.out = s.y.as<float>(); aa.ldo = L.ng;
             aa.rel = W.rel.as<float>(); aa.bucket_of = S.bucket_of.as<int32_t>();
@@ -191,7 +213,7 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
             aa.partial = state.attn_partial.as<float>();
             B2_TRY(attn_prepare_f32(aa, st));
             B2_TRY(attn_bias_f32(aa, st));
-            B2_TRY(sigmoid_gate_f32(s.y.as<float>(), L.ng, proj + L.nq + L.nk + L.nv, L.lproj, s.gated.as<float>(), L.ng, R, L.ng, st));
+            B2_TRY(sigmoid_gate_f32(s.y.as<float>(), L.ng, proj + L.nq + L.nk + L.nv, L.lproj_ld, s.gated.as<float>(), L.ng, R, L.ng, st));
             B2_TRY(lin(s.gated.as<float>(), L.ng, W.lo_w, width, L.ng, mix, width, R, LIN_NONE, d.left_scale));
             // ---- right: RWKV time mixing -------------------------------------------------------------------------------
             const size_t ms = (size_t)s.rows * width;  // stride between the five mixes (r, k, v, g, w)
@@ -257,7 +279,7 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     const int width = s.d.width, V = s.d.vocab, WD = s.w_dtype;
     const std::string k(key);
     if (k == "embed") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.embed, WD, (size_t)V * width, 0, ptr, dt, (int64_t)V * width); }
-    if (k == "head") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.head, WD, (size_t)V * width, 0, ptr, dt, (int64_t)V * width); }
+    if (k == "head") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.head, WD, (size_t)((V + 7) / 8 * 8) * width, 0, ptr, dt, (int64_t)V * width); }
     if (k == "final.norm") { B2_TRY(want_shape(key, shape, ndim, width)); s.got[k] = 1; return put_tensor(s.final_w, DT_F32, width, 0, ptr, dt, width); }
     if (k == "final.norm.b") { B2_TRY(want_shape(key, shape, ndim, width)); s.got[k] = 1; return put_tensor(s.final_b, DT_F32, width, 0, ptr, dt, width); }
     int li = -1, used = 0;
@@ -271,7 +293,8 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     SeqWeights& W = s.w[li];
     const std::string r = k.substr(used);
     auto vec = [&](DevBuf& b, int64_t n) -> int { B2_TRY(want_shape(key, shape, ndim, n)); W.got[r] = 1; return put_tensor(b, DT_F32, n, 0, ptr, dt, n); };
-    auto mat = [&](DevBuf& b, int64_t o, int64_t i) -> int { B2_TRY(want_shape(key, shape, ndim, o, i)); W.got[r] = 1; return put_tensor(b, WD, (size_t)o * i, 0, ptr, dt, o * i); };
+    // Linear weights are allocated with their rows padded to a multiple of 8 (zeros): the tensor-core GEMM wants N % 8 == 0
+    auto mat = [&](DevBuf& b, int64_t o, int64_t i) -> int { B2_TRY(want_shape(key, shape, ndim, o, i)); W.got[r] = 1; return put_tensor(b, WD, (size_t)((o + 7) / 8 * 8) * i, 0, ptr, dt, o * i); };
     if (r == "norm1") return vec(W.norm1, width);
     if (r == "norm1.b") return vec(W.norm1_b, width);
     if (d.ff > 0) {
@@ -298,7 +321,7 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
             if (r == parts[j]) {
                 B2_TRY(want_shape(key, shape, ndim, sizes[j], width));
                 W.got[r] = 1;
-                return put_tensor(W.lproj_w, WD, (size_t)L.lproj * width, row0 * width, ptr, dt, (int64_t)sizes[j] * width);
+                return put_tensor(W.lproj_w, WD, (size_t)L.lproj_ld * width, row0 * width, ptr, dt, (int64_t)sizes[j] * width);
             }
             row0 += sizes[j];
         }
@@ -358,9 +381,9 @@ int seq_finalize(b2_model* m) {
     int pw = 1, aw = 1, yw = 1, rw = 1, kw = 1, fw = 1;
     for (const SeqLayerInfo& L : s.layers) {
         if (L.d.type == B2_MIXER_MAMBA2) {
-            pw = std::max(pw, L.dproj); aw = std::max(aw, L.conv_ch); yw = std::max(yw, L.inner);
+            pw = std::max(pw, L.dproj_ld); aw = std::max(aw, L.conv_ch); yw = std::max(yw, L.inner);
         } else {
-            pw = std::max(pw, L.lproj); yw = std::max(yw, std::max(L.ng, L.rn)); rw = std::max(rw, L.rn); kw = std::max(kw, L.d.r_decay_rank);
+            pw = std::max(pw, L.lproj_ld); yw = std::max(yw, std::max(L.ng, L.rn)); rw = std::max(rw, L.rn); kw = std::max(kw, L.d.r_decay_rank);
         }
         fw = std::max(fw, L.d.ff);
     }
@@ -378,6 +401,12 @@ int seq_finalize(b2_model* m) {
     B2_TRY(s.wlog.alloc(R * rw * F4));
     B2_TRY(s.ff.alloc(R * fw * F4));
     B2_TRY(s.xn.alloc(R * width * F4));
+    {
+        int kmax = width;
+        for (const SeqLayerInfo& L : s.layers) kmax = std::max(kmax, std::max(std::max(L.inner, L.ng), std::max(L.rn, L.d.ff)));
+        s.a16_w = (kmax + 7) / 8 * 8;
+        if (s.d.compute == B2_COMPUTE_BF16) B2_TRY(s.a16.alloc(R * s.a16_w * 2));
+    }
     B2_TRY(s.tok.alloc(R * 4));
     B2_TRY(s.want.alloc(R * 4));
     B2_TRY(s.segs.alloc((size_t)std::max(1, s.d.max_batch) * sizeof(SeqSeg)));
@@ -397,7 +426,7 @@ void seq_model_free(b2_model* m) {
         for (DevBuf* b : bs) b->free();
     }
     DevBuf* bs[] = {&s.embed, &s.head, &s.final_w, &s.final_b, &s.x, &s.proj, &s.act, &s.y, &s.gated, &s.mixout, &s.mixes, &s.rp, &s.wl1, &s.wlog,
-                    &s.ff, &s.xn, &s.tok, &s.want, &s.segs, &s.row_slot, &s.row_pos};
+                    &s.ff, &s.xn, &s.tok, &s.want, &s.segs, &s.row_slot, &s.row_pos, &s.a16};
     for (DevBuf* b : bs) b->free();
     delete m->seq;
     m->seq = nullptr;
@@ -511,6 +540,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             L.inner = l.m_heads * l.m_vdim;
             L.conv_ch = L.inner + 2 * l.m_groups * l.m_state;
             L.dproj = 2 * L.inner + 2 * l.m_groups * l.m_state + l.m_heads;
+            L.dproj_ld = (L.dproj + 7) / 8 * 8;
         } else if (l.type == B2_MIXER_PARALLEL) {
             if (l.a_heads < 1 || l.a_kv_heads < 1 || l.a_heads % l.a_kv_heads) why = "attention: heads must be a positive multiple of kv_heads";
             else if (l.a_dim < 1 || l.a_dim > 256 || l.a_vdim < 1 || l.a_vdim > 256) why = "attention: head sizes 1..256";
@@ -519,6 +549,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             else if (l.r_heads < 1 || l.r_dim < 1 || l.r_dim > 256 || l.r_decay_rank < 1) why = "rwkv: heads, dim 1..256, decay rank";
             L.nq = l.a_heads * l.a_dim; L.nk = l.a_kv_heads * l.a_dim; L.nv = l.a_kv_heads * l.a_vdim; L.ng = l.a_heads * l.a_vdim;
             L.lproj = L.nq + L.nk + L.nv + L.ng;
+            L.lproj_ld = (L.lproj + 7) / 8 * 8;
             L.rn = l.r_heads * l.r_dim;
         } else {
             why = "unknown mixer type";

@@ -194,4 +194,4 @@ def random_weights(cfg, seed=0, scale=1.0):
             ff = layer["mlp"]["ff"]
             w[p + "norm2"], w[p + "norm2.b"] = 1 + rnd(width, s=0.1), rnd(width, s=0.1)
             w[p + "mlp.up"], w[p + "mlp.down"] = rnd(ff, width, s=ws), rnd(width, ff, s=ff ** -0.5)
-    return w
+    return {k: v.bfloat16().float() for k, v in w.items()}
