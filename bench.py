@@ -776,7 +776,8 @@ def run_katadra(args):
     from llava._b2 import LOGITS_LAST, launch_count
 
     dev = torch.device("cuda:0")
-    pk = peaks()
+    hbm, tfl, src = peaks()
+    pk = {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}
     S, N, layers = args.ctx, 64, 4
     flush = torch.zeros(160 * 1024 * 1024 // 4, device=dev)  # 160 MB > 126 MB of L2
     out = {"metric": "layer-list decoder vs LLaMA decoder at equal size", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",

@@ -138,6 +138,130 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
     }
 }
 
+// ---- tiled kernel: a CTA takes a tile of query rows of ONE slot x one key/value head x one key split. Keys and values are
+// staged 32 at a time in shared memory with coalesced loads and shared by every (query row, query head of the group) pair of
+// the CTA, so a key/value row crosses the memory system once per CTA instead of once per pair. 8 warps, <= 4 pairs per warp.
+constexpr int TL_KT = 32, TL_WARPS = 8, TL_PPW = 4;
+
+template <bool VEC>
+__global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a, int QT) {
+    extern __shared__ float sm[];
+    const int HG = a.H / a.G, g = blockIdx.y, sp = blockIdx.z;
+    const int r0 = blockIdx.x * QT, nrows = min(QT, a.rows - r0), P = nrows * HG;
+    const int dk = a.dk, dv = a.dv, dkp = VEC ? dk + 4 : (dk | 1);
+    float* sQ = sm;                              // [QT * HG][dk]
+    float* sK = sQ + (size_t)QT * HG * dk;       // [TL_KT][dkp]
+    float* sV = sK + TL_KT * dkp;                // [TL_KT][dv]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+    const int slot = a.row_slot[r0];
+    int maxpos = -1;
+    for (int i = 0; i < nrows; ++i) maxpos = max(maxpos, a.row_pos[r0 + i]);
+    if (maxpos < 0) return;
+    for (int e = tid; e < P * dk; e += TL_WARPS * 32) {
+        const int p = e / dk, d = e % dk;
+        sQ[e] = a.q[(size_t)(r0 + p / HG) * a.ldq + (size_t)(g * HG + p % HG) * dk + d];
+    }
+    int lo = 0, hi = maxpos + 1;
+    if (a.nsplit > 1) {
+        const int per = ((maxpos + a.nsplit) / a.nsplit + TL_KT - 1) / TL_KT * TL_KT;
+        lo = sp * per;
+        hi = min(maxpos + 1, lo + per);
+    }
+    const float* K = a.kcache + ((size_t)slot * a.G + g) * a.Smax * dk;
+    const float* V = a.vcache + ((size_t)slot * a.G + g) * a.Smax * dv;
+    float m[TL_PPW], l[TL_PPW], o[TL_PPW][AT_MAXC];
+    int ppos[TL_PPW];
+#pragma unroll
+    for (int i = 0; i < TL_PPW; ++i) {
+        m[i] = -INFINITY; l[i] = 0.f;
+        const int p = warp + TL_WARPS * i;
+        ppos[i] = p < P ? a.row_pos[r0 + p / HG] : -1;
+#pragma unroll
+        for (int c = 0; c < AT_MAXC; ++c) o[i][c] = 0.f;
+    }
+    for (int j0 = lo; j0 < hi; j0 += TL_KT) {
+        const int nk = min(TL_KT, hi - j0);
+        __syncthreads();
+        if (VEC) {
+            const int dk4 = dk >> 2;
+            for (int e = tid; e < nk * dk4; e += TL_WARPS * 32) {
+                const int kk = e / dk4, d4 = e % dk4;
+                *reinterpret_cast<float4*>(sK + kk * dkp + d4 * 4) = *reinterpret_cast<const float4*>(K + (size_t)(j0 + kk) * dk + d4 * 4);
+            }
+        } else {
+            for (int e = tid; e < nk * dk; e += TL_WARPS * 32) sK[(e / dk) * dkp + e % dk] = K[(size_t)j0 * dk + e];
+        }
+        for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)j0 * dv + e];
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < TL_PPW; ++i) {
+            const int p = warp + TL_WARPS * i;
+            const int pos = ppos[i];
+            if (pos < j0) continue;                    // idle pair, or every key of the tile is in its future (warp-uniform)
+            const int head = g * HG + p % HG;
+            const int j = j0 + lane;
+            const bool valid = lane < nk && j <= pos;
+            float s = -INFINITY;
+            if (valid) {
+                const float* q = sQ + p * dk;
+                const float* kr = sK + lane * dkp;
+                float acc = 0.f;
+                if (VEC) {
+                    for (int d = 0; d < dk; d += 4) {
+                        const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+                        const float4 qv = *reinterpret_cast<const float4*>(q + d);
+                        acc = fmaf(qv.x, kv.x, acc); acc = fmaf(qv.y, kv.y, acc); acc = fmaf(qv.z, kv.z, acc); acc = fmaf(qv.w, kv.w, acc);
+                    }
+                } else {
+                    for (int d = 0; d < dk; ++d) acc = fmaf(q[d], kr[d], acc);
+                }
+                s = acc * a.scale;
+                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+                s += a.rel[(size_t)a.bucket_of[pos - j] * a.H + head];
+            }
+            const float m_new = fmaxf(m[i], warp_max(s));
+            const float pr = valid ? expf(s - m_new) : 0.f;
+            const float corr = expf(m[i] - m_new);
+            l[i] = fmaf(l[i], corr, warp_sum(pr));
+            m[i] = m_new;
+#pragma unroll
+            for (int c = 0; c < AT_MAXC; ++c) o[i][c] *= corr;
+            const int nv = min(nk, pos - j0 + 1);
+            for (int jj = 0; jj < nv; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, pr, jj);
+                const float* vr = sV + jj * dv;
+#pragma unroll
+                for (int c = 0; c < AT_MAXC; ++c) {
+                    const int d = lane + 32 * c;
+                    if (d < dv) o[i][c] = fmaf(pj, vr[d], o[i][c]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TL_PPW; ++i) {
+        const int p = warp + TL_WARPS * i;
+        if (p >= P || ppos[i] < 0) continue;
+        const int row = r0 + p / HG, head = g * HG + p % HG;
+        if (a.nsplit > 1) {
+            float* part = a.partial + ((size_t)(row * a.H + head) * a.nsplit + sp) * (dv + 2);
+            if (lane == 0) { part[0] = m[i]; part[1] = l[i]; }
+#pragma unroll
+            for (int c = 0; c < AT_MAXC; ++c) {
+                const int d = lane + 32 * c;
+                if (d < dv) part[2 + d] = o[i][c];
+            }
+        } else {
+            const float inv = 1.f / l[i];
+#pragma unroll
+            for (int c = 0; c < AT_MAXC; ++c) {
+                const int d = lane + 32 * c;
+                if (d < dv) a.out[(size_t)row * a.ldo + (size_t)head * dv + d] = o[i][c] * inv;
+            }
+        }
+    }
+}
+
 // one warp per (row, head): combines the key splits in split order
 __global__ void attn_merge_kernel(BiasAttnArgs a) {
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -185,6 +309,29 @@ int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t st) {
     B2_CHECK_ARG(a.nsplit >= 1 && (a.nsplit == 1 || a.partial != nullptr), "attn_bias: key splits without scratch");
     const int warps = a.rows * a.H;
     const bool vec = a.dk % 4 == 0 && (reinterpret_cast<uintptr_t>(a.kcache) & 15) == 0;
+    const int HG = a.H / a.G;
+    if (HG <= TL_WARPS * TL_PPW && a.tile_rows >= 1) {
+        // query rows per CTA: as many as the 32 (row, head) pairs of a CTA allow; rows of a tile share their slot (tile_rows
+        // is 1 for a decode step, where every row has its own)
+        int QT = (TL_WARPS * TL_PPW) / HG;
+        if (QT > a.tile_rows) QT = a.tile_rows;
+        const int dkp = vec ? a.dk + 4 : (a.dk | 1);
+        const size_t smem = ((size_t)QT * HG * a.dk + (size_t)TL_KT * dkp + (size_t)TL_KT * a.dv) * sizeof(float);
+        dim3 grid((a.rows + QT - 1) / QT, a.G, a.nsplit);
+        if (vec) {
+            if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attn_tile_kernel<true><<<grid, TL_WARPS * 32, smem, st>>>(a, QT);
+        } else {
+            if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attn_tile_kernel<false><<<grid, TL_WARPS * 32, smem, st>>>(a, QT);
+        }
+        B2_LAUNCH_CHECK();
+        if (a.nsplit > 1) {
+            attn_merge_kernel<<<(warps + 7) / 8, 256, 0, st>>>(a);
+            B2_LAUNCH_CHECK();
+        }
+        return 0;
+    }
     dim3 grid((warps + AT_WARPS - 1) / AT_WARPS, a.nsplit);
     const size_t smem = (size_t)AT_WARPS * a.dk * sizeof(float);
     if (vec) attn_bias_kernel<true><<<grid, AT_WARPS * 32, smem, st>>>(a);

@@ -307,12 +307,13 @@ int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, f
 // Causal depthwise convolution + SiLU with a carried tail: out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]);
 // inputs before the start of the call come from tail[slot][taps-1][C] (zeros when the segment starts a sequence); the tail is
 // replaced by the last taps-1 inputs. taps <= 8.
+// max_n: the longest segment of the call (the launch grid covers that many rows per segment).
 int causal_conv_silu_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C,
-                         int taps, const SeqSeg* segs, int nseg, cudaStream_t stream);
+                         int taps, const SeqSeg* segs, int nseg, int max_n, cudaStream_t stream);
 // Token shift: out[s][t, c] = x[t, c] + (x[t-1, c] - x[t, c]) * mu[s][c] for s < n_mix, with x[-1] = prev[slot] (zeros at a sequence
 // start); prev[slot] := the segment's last row. out is [n_mix][rows_total][cols].
 int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out, int64_t out_stride, int cols, int n_mix, const SeqSeg* segs,
-                        int nseg, cudaStream_t stream);
+                        int nseg, int max_n, cudaStream_t stream);
 // Linear recurrence with a diagonal decay over a [key, value] state per head, carried per slot in fp32:
 //   SCAN_SSD : dt = softplus(dt_raw + dt_bias[h]); S = exp(-exp(a_log[h]) dt) S + (dt k) v^T ; y = S^T q + skip[h] v
 //              (q, k: [rows, groups, dk] shared by heads/groups consecutive heads; v: [rows, heads, dv])
@@ -345,6 +346,8 @@ struct BiasAttnArgs {
     float temp_coef = 0.f, temp_every = 1.f;      // q *= 1 + coef * ln(floor((p + 1) / every) + 1)
     const int32_t* row_slot = nullptr; const int32_t* row_pos = nullptr;
     float* partial = nullptr; int nsplit = 1;     // split-KV scratch [rows*H*nsplit*(dv+2)] when nsplit > 1
+    int tile_rows = 0;                            // consecutive rows that share a slot (a prompt portion: its rows; a decode step: 1);
+                                                  // 0: one warp per (row, head) without shared key/value tiles
 };
 int attn_prepare_f32(const BiasAttnArgs& a, cudaStream_t stream);  // q/k norms, temperature, cache append
 int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t stream);     // causal softmax attention of every row against its slot's cache

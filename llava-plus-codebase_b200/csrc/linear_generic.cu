@@ -2,6 +2,8 @@
 // true-fp32 compute: a weight-streaming row kernel for a handful of rows (decode) and a shared-memory tiled kernel for
 // portions of a prompt. Accumulation is fp32 FMA in both; with round_a the activations are rounded to bf16 first, so the
 // product is the bf16 x bf16 -> fp32 product the tensor-core path computes.
+#include <algorithm>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -41,7 +43,65 @@ __device__ __forceinline__ void ld_w8(const __nv_bfloat16* p, float (&w)[8]) {
     w[4] = __uint_as_float(t.z << 16); w[5] = __uint_as_float(t.z & 0xffff0000u);
     w[6] = __uint_as_float(t.w << 16); w[7] = __uint_as_float(t.w & 0xffff0000u);
 }
-template <typename TW, bool VEC>
+// VEC kernel: a CTA of 8 warps takes 32 output columns (4 per warp, so a lane keeps 4 weight loads of 16 B in flight) and
+// stages the activation rows once in shared memory, KC columns at a time, already rounded to bf16 when the product is bf16.
+constexpr int RW_COLS = 4, RW_KC = 2048;
+template <typename TW>
+__global__ void __launch_bounds__(256) linear_rows_vec_kernel(const float* __restrict__ A, int64_t lda, const TW* __restrict__ W, int64_t ldw,
+                                                              const float* __restrict__ bias, float* __restrict__ out, int64_t ld_out, int M, int N,
+                                                              int K, int act, float alpha, int accumulate, int round_a) {
+    extern __shared__ float sA[];  // [M][kc]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * 8 + warp) * RW_COLS;
+    float acc[RW_COLS][MR];
+#pragma unroll
+    for (int c = 0; c < RW_COLS; ++c)
+#pragma unroll
+        for (int m = 0; m < MR; ++m) acc[c][m] = 0.f;
+    for (int kc0 = 0; kc0 < K; kc0 += RW_KC) {
+        const int kc = min(RW_KC, K - kc0);
+        __syncthreads();
+        for (int e = threadIdx.x * 4; e < M * kc; e += 1024) {
+            const int m = e / kc, k = e % kc;
+            float4 v = *reinterpret_cast<const float4*>(A + (size_t)m * lda + kc0 + k);
+            if (round_a) { v.x = round_bf16(v.x); v.y = round_bf16(v.y); v.z = round_bf16(v.z); v.w = round_bf16(v.w); }
+            *reinterpret_cast<float4*>(sA + e) = v;
+        }
+        __syncthreads();
+        for (int k = lane * 8; k < kc; k += 256) {
+            float wv[RW_COLS][8];
+#pragma unroll
+            for (int c = 0; c < RW_COLS; ++c) {
+                // columns past N read the last row again: their sums are never stored
+                const int n = min(n0 + c, N - 1);
+                ld_w8(W + (size_t)n * ldw + kc0 + k, wv[c]);
+            }
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+                if (m < M) {
+                    float av[8];
+                    ld_w8(sA + m * kc + k, av);
+#pragma unroll
+                    for (int c = 0; c < RW_COLS; ++c)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[c][m] = fmaf(av[e], wv[c][e], acc[c][m]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < RW_COLS; ++c)
+#pragma unroll
+        for (int m = 0; m < MR; ++m) {
+            float v = acc[c][m];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && m < M && n0 + c < N) lin_store(out + (size_t)m * ld_out + n0 + c, v, bias, n0 + c, act, alpha, accumulate);
+        }
+}
+
+// any K and alignment: one warp per output column, scalar loads
+template <typename TW>
 __global__ void __launch_bounds__(256) linear_rows_kernel(const float* __restrict__ A, int64_t lda, const TW* __restrict__ W, int64_t ldw,
                                                           const float* __restrict__ bias, float* __restrict__ out, int64_t ld_out, int M, int N,
                                                           int K, int act, float alpha, int accumulate, int round_a) {
@@ -52,38 +112,14 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const float* __restric
     float acc[MR];
 #pragma unroll
     for (int m = 0; m < MR; ++m) acc[m] = 0.f;
-    if (VEC) {
-        for (int k0 = lane * 8; k0 < K; k0 += 512) {
-            float wv[2][8];
-            const int k1 = k0 + 256;
-            ld_w8(w + k0, wv[0]);
-            if (k1 < K) ld_w8(w + k1, wv[1]);
+    for (int k = lane; k < K; k += 32) {
+        const float wv = ld_w(w + k);
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                const int k = u == 0 ? k0 : k1;
-                if (k < K) {
-#pragma unroll
-                    for (int m = 0; m < MR; ++m) {
-                        if (m < M) {
-                            float av[8];
-                            ld_w8(A + (size_t)m * lda + k, av);
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) acc[m] = fmaf(round_a ? round_bf16(av[e]) : av[e], wv[u][e], acc[m]);
-                        }
-                    }
-                }
-            }
-        }
-    } else {
-        for (int k = lane; k < K; k += 32) {
-            const float wv = ld_w(w + k);
-#pragma unroll
-            for (int m = 0; m < MR; ++m) {
-                if (m < M) {
-                    float a = A[(size_t)m * lda + k];
-                    if (round_a) a = round_bf16(a);
-                    acc[m] = fmaf(a, wv, acc[m]);
-                }
+        for (int m = 0; m < MR; ++m) {
+            if (m < M) {
+                float a = A[(size_t)m * lda + k];
+                if (round_a) a = round_bf16(a);
+                acc[m] = fmaf(a, wv, acc[m]);
             }
         }
     }
@@ -157,13 +193,19 @@ int launch_linear(const LinearArgs& a, cudaStream_t st) {
     if (a.M <= MR) {
         const bool vec = a.K % 8 == 0 && a.lda % 4 == 0 && a.ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(a.W) & 15) == 0;
-        dim3 grid((a.N + 7) / 8);
-        if (vec)
-            linear_rows_kernel<TW, true><<<grid, 256, 0, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M, a.N, a.K, a.act, a.alpha,
-                                                               a.accumulate, a.round_a);
-        else
-            linear_rows_kernel<TW, false><<<grid, 256, 0, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M, a.N, a.K, a.act, a.alpha,
-                                                                a.accumulate, a.round_a);
+        if (vec) {
+            const size_t smem = (size_t)a.M * std::min(RW_KC, a.K) * sizeof(float);
+            static bool attr_set = false;
+            if (!attr_set) {
+                B2_CUDA_CHECK(cudaFuncSetAttribute(linear_rows_vec_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, MR * RW_KC * 4));
+                attr_set = true;
+            }
+            linear_rows_vec_kernel<TW><<<(a.N + 8 * RW_COLS - 1) / (8 * RW_COLS), 256, smem, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M,
+                                                                                                  a.N, a.K, a.act, a.alpha, a.accumulate, a.round_a);
+        } else {
+            linear_rows_kernel<TW><<<(a.N + 7) / 8, 256, 0, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M, a.N, a.K, a.act, a.alpha,
+                                                                 a.accumulate, a.round_a);
+        }
     } else {
         dim3 grid((a.N + TB - 1) / TB, (a.M + TB - 1) / TB);
         linear_tiled_kernel<TW><<<grid, 256, 0, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M, a.N, a.K, a.act, a.alpha,

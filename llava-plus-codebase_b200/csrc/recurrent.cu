@@ -12,41 +12,47 @@ namespace {
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-// ---- causal depthwise convolution + SiLU: one thread per channel walks its segment with the window in registers --------
-constexpr int CONV_MAX_TAPS = 8, CONV_UNROLL = 8;
+// ---- causal depthwise convolution + SiLU -----------------------------------------------------------------------------------
+// One thread per (channel, tile of CONV_TILE tokens): it primes its window from the inputs in front of the tile (rows of this
+// call, or the carried tail for positions before the call) and walks the tile. The compute kernel only READS the tail; a
+// second small kernel replaces it afterwards, so tiles never race with the update.
+constexpr int CONV_MAX_TAPS = 8, CONV_TILE = 32;
 __global__ void __launch_bounds__(128) causal_conv_silu_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ w,
-                                                               const float* __restrict__ bias, float* __restrict__ tail, float* __restrict__ out,
-                                                               int64_t ld_out, int C, int taps, const SeqSeg* __restrict__ segs) {
-    const SeqSeg sg = segs[blockIdx.y];
+                                                               const float* __restrict__ bias, const float* __restrict__ tail,
+                                                               float* __restrict__ out, int64_t ld_out, int C, int taps,
+                                                               const SeqSeg* __restrict__ segs) {
+    const SeqSeg sg = segs[blockIdx.z];
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C || sg.n <= 0) return;
+    const int tt0 = blockIdx.y * CONV_TILE;
+    if (c >= C || tt0 >= sg.n) return;
     // Window and taps are kept right-aligned in arrays of CONV_MAX_TAPS (all indices static): entry CONV_MAX_TAPS-1 is the
     // current token, the unused leading entries carry zero weights.
     float wt[CONV_MAX_TAPS], win[CONV_MAX_TAPS];
+    const float* tl = tail + (size_t)sg.slot * (taps - 1) * C + c;
+    const float* ip = in + (size_t)sg.row0 * ld_in + c;
 #pragma unroll
     for (int jp = 0; jp < CONV_MAX_TAPS; ++jp) {
         const int tj = jp - (CONV_MAX_TAPS - taps);
         wt[jp] = tj >= 0 ? w[(size_t)c * taps + tj] : 0.f;
-        win[jp] = 0.f;
-    }
-    float* tl = tail + (size_t)sg.slot * (taps - 1) * C + c;
-    if (sg.pos0 > 0) {
-#pragma unroll
-        for (int jp = 1; jp < CONV_MAX_TAPS; ++jp) {
-            const int j = jp - (CONV_MAX_TAPS - (taps - 1));
-            if (j >= 0) win[jp] = tl[(size_t)j * C];
+        // primed one step early (the loop shifts before it appends): entry jp holds the input of token tt0 - (CONV_MAX_TAPS - jp)
+        const int t = tt0 - (CONV_MAX_TAPS - jp);
+        float v = 0.f;
+        if (jp >= CONV_MAX_TAPS - (taps - 1)) {  // the taps-1 tokens in front of the tile
+            if (t >= 0) v = ip[(size_t)t * ld_in];
+            else if (sg.pos0 > 0) v = tl[(size_t)(t + (taps - 1)) * C];
         }
+        win[jp] = v;
     }
     const float b = bias[c];
-    const float* ip = in + (size_t)sg.row0 * ld_in + c;
     float* op = out + (size_t)sg.row0 * ld_out + c;
-    for (int t0 = 0; t0 < sg.n; t0 += CONV_UNROLL) {
-        float v[CONV_UNROLL];
+    const int t_end = min(sg.n, tt0 + CONV_TILE);
+    for (int t0 = tt0; t0 < t_end; t0 += 8) {
+        float v[8];
 #pragma unroll
-        for (int u = 0; u < CONV_UNROLL; ++u) v[u] = t0 + u < sg.n ? ip[(size_t)(t0 + u) * ld_in] : 0.f;
+        for (int u = 0; u < 8; ++u) v[u] = t0 + u < t_end ? ip[(size_t)(t0 + u) * ld_in] : 0.f;
 #pragma unroll
-        for (int u = 0; u < CONV_UNROLL; ++u) {
-            if (t0 + u < sg.n) {
+        for (int u = 0; u < 8; ++u) {
+            if (t0 + u < t_end) {
 #pragma unroll
                 for (int jp = 0; jp < CONV_MAX_TAPS - 1; ++jp) win[jp] = win[jp + 1];
                 win[CONV_MAX_TAPS - 1] = v[u];
@@ -57,48 +63,67 @@ __global__ void __launch_bounds__(128) causal_conv_silu_kernel(const float* __re
             }
         }
     }
-#pragma unroll
-    for (int jp = 1; jp < CONV_MAX_TAPS; ++jp) {
-        const int j = jp - (CONV_MAX_TAPS - (taps - 1));
-        if (j >= 0) tl[(size_t)j * C] = win[jp];
-    }
 }
-
-// ---- token shift: out[s][t] = x[t] + (x[t-1] - x[t]) * mu[s] ------------------------------------------------------------
-constexpr int SHIFT_MAX_MIX = 8;
-__global__ void __launch_bounds__(128) token_shift_mix_kernel(const float* __restrict__ x, const float* __restrict__ mu, float* __restrict__ prev,
-                                                              float* __restrict__ out, int64_t out_stride, int cols, int n_mix,
-                                                              const SeqSeg* __restrict__ segs) {
+// tail[j] := input of token n - (taps-1) + j of the segment; tokens before the call come from the old tail (or zero)
+__global__ void __launch_bounds__(128) causal_conv_tail_kernel(const float* __restrict__ in, int64_t ld_in, float* __restrict__ tail, int C,
+                                                               int taps, const SeqSeg* __restrict__ segs) {
     const SeqSeg sg = segs[blockIdx.y];
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= cols || sg.n <= 0) return;
+    if (c >= C || sg.n <= 0) return;
+    float* tl = tail + (size_t)sg.slot * (taps - 1) * C + c;
+    float nv[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+        nv[j] = 0.f;
+        if (j < taps - 1) {
+            const int t = sg.n - (taps - 1) + j;
+            if (t >= 0) nv[j] = in[(size_t)(sg.row0 + t) * ld_in + c];
+            else if (sg.pos0 > 0) nv[j] = tl[(size_t)(t + (taps - 1)) * C];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+        if (j < taps - 1) tl[(size_t)j * C] = nv[j];
+}
+
+// ---- token shift: out[s][t] = x[t] + (x[t-1] - x[t]) * mu[s]; x[-1] of a call is the carried row (zero at a sequence start) ---
+constexpr int SHIFT_MAX_MIX = 8, SHIFT_TILE = 8;
+__global__ void __launch_bounds__(128) token_shift_mix_kernel(const float* __restrict__ x, const float* __restrict__ mu,
+                                                              const float* __restrict__ prev, float* __restrict__ out, int64_t out_stride,
+                                                              int cols, int n_mix, const SeqSeg* __restrict__ segs) {
+    const SeqSeg sg = segs[blockIdx.z];
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t0 = blockIdx.y * SHIFT_TILE;
+    if (c >= cols || t0 >= sg.n) return;
     float m[SHIFT_MAX_MIX];
 #pragma unroll
     for (int s = 0; s < SHIFT_MAX_MIX; ++s) m[s] = s < n_mix ? mu[(size_t)s * cols + c] : 0.f;
-    float last = sg.pos0 > 0 ? prev[(size_t)sg.slot * cols + c] : 0.f;
-    for (int t0 = 0; t0 < sg.n; t0 += 8) {
-        float v[8];
+    float v[SHIFT_TILE + 1];
+    v[0] = t0 > 0 ? x[(size_t)(sg.row0 + t0 - 1) * cols + c] : (sg.pos0 > 0 ? prev[(size_t)sg.slot * cols + c] : 0.f);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) v[u] = t0 + u < sg.n ? x[(size_t)(sg.row0 + t0 + u) * cols + c] : 0.f;
+    for (int u = 0; u < SHIFT_TILE; ++u) v[u + 1] = t0 + u < sg.n ? x[(size_t)(sg.row0 + t0 + u) * cols + c] : 0.f;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-            if (t0 + u < sg.n) {
-                const float d = last - v[u];
+    for (int u = 0; u < SHIFT_TILE; ++u) {
+        if (t0 + u < sg.n) {
+            const float d = v[u] - v[u + 1];
 #pragma unroll
-                for (int s = 0; s < SHIFT_MAX_MIX; ++s)
-                    if (s < n_mix) out[(size_t)s * out_stride + (size_t)(sg.row0 + t0 + u) * cols + c] = fmaf(d, m[s], v[u]);
-                last = v[u];
-            }
+            for (int s = 0; s < SHIFT_MAX_MIX; ++s)
+                if (s < n_mix) out[(size_t)s * out_stride + (size_t)(sg.row0 + t0 + u) * cols + c] = fmaf(d, m[s], v[u + 1]);
         }
     }
-    prev[(size_t)sg.slot * cols + c] = last;
+}
+__global__ void __launch_bounds__(128) token_shift_carry_kernel(const float* __restrict__ x, float* __restrict__ prev, int cols,
+                                                                const SeqSeg* __restrict__ segs) {
+    const SeqSeg sg = segs[blockIdx.y];
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < cols && sg.n > 0) prev[(size_t)sg.slot * cols + c] = x[(size_t)(sg.row0 + sg.n - 1) * cols + c];
 }
 
 // ---- linear recurrence ------------------------------------------------------------------------------------------------
 // Block = 32 value columns (threadIdx.x) x KS key slices (threadIdx.y) of one head of one segment. A thread keeps KPT keys
 // of its column's state in registers. Tokens are staged TT at a time into shared memory with the per-token preparation done
-// while staging (step size, decay, dt-scaled key), then walked in order; the KS partial dot products of a token meet in a
-// double-buffered shared array (one barrier per token).
+// while staging (step size, decay, dt-scaled key), then walked in order with no barrier in between: the recurrence lives in
+// registers, and the KS partial dot products of the tile's tokens meet in shared memory once per tile.
 constexpr int KPT = 16, TT = 16;
 
 template <int MODE>
@@ -113,7 +138,7 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
     float* sK = sQ + TT * dkp;         // [TT][dkp]
     float* sD = sK + TT * dkp;         // [TT][dkp] decay per key channel
     float* sV = sD + TT * dkp;         // [TT][32]
-    float* sR = sV + TT * 32;          // [2][KS][32]
+    float* sR = sV + TT * 32;          // [TT][KS][32] partial outputs of a tile
     const int g = MODE == SCAN_SSD ? h / (a.heads / a.groups) : h;
     const bool col_ok = j < dv;
     float S[KPT], bon[KPT];
@@ -152,36 +177,51 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
             sV[e] = jj < dv ? a.v[(size_t)(sg.row0 + t0 + t) * a.ldv + (size_t)h * dv + jj] : 0.f;
         }
         __syncthreads();
-        for (int t = 0; t < nt; ++t) {
-            const float v = sV[t * 32 + threadIdx.x];
-            const float* q = sQ + t * dkp + ks * KPT;
-            const float* k = sK + t * dkp + ks * KPT;
-            const float* d = sD + t * dkp + ks * KPT;
-            float acc = 0.f;
+        float part[TT];   // this thread's share of y[t][j] for the tokens of the tile
 #pragma unroll
-            for (int i = 0; i < KPT; ++i) {
-                const float kv = k[i] * v;
-                if (MODE == SCAN_RWKV) {
-                    acc = fmaf(q[i], fmaf(bon[i], kv, S[i]), acc);
-                    S[i] = fmaf(d[i], S[i], kv);
-                } else {
-                    S[i] = fmaf(d[i], S[i], kv);
-                    acc = fmaf(q[i], S[i], acc);
+        for (int t = 0; t < TT; ++t) {
+            part[t] = 0.f;
+            if (t < nt) {
+                const float v = sV[t * 32 + threadIdx.x];
+                const float* q = sQ + t * dkp + ks * KPT;
+                const float* k = sK + t * dkp + ks * KPT;
+                const float* d = sD + t * dkp + ks * KPT;
+                float acc = 0.f;
+#pragma unroll
+                for (int i = 0; i < KPT; ++i) {
+                    const float kv = k[i] * v;
+                    if (MODE == SCAN_RWKV) {
+                        acc = fmaf(q[i], fmaf(bon[i], kv, S[i]), acc);
+                        S[i] = fmaf(d[i], S[i], kv);
+                    } else {
+                        S[i] = fmaf(d[i], S[i], kv);
+                        acc = fmaf(q[i], S[i], acc);
+                    }
+                }
+                part[t] = acc;
+            }
+        }
+        // the key slices meet once per tile: partial sums through shared memory, every thread finishes some (token, column) pairs
+        if (KS > 1) {
+#pragma unroll
+            for (int t = 0; t < TT; ++t) sR[(t * KS + ks) * 32 + threadIdx.x] = part[t];
+            __syncthreads();
+            for (int t = ks; t < nt; t += KS) {
+                float acc = 0.f;
+                for (int s2 = 0; s2 < KS; ++s2) acc += sR[(t * KS + s2) * 32 + threadIdx.x];
+                if (col_ok) {
+                    if (MODE == SCAN_SSD) acc = fmaf(skip, sV[t * 32 + threadIdx.x], acc);
+                    a.y[(size_t)(sg.row0 + t0 + t) * a.ldy + (size_t)h * dv + j] = acc;
                 }
             }
-            float* red = sR + ((t0 + t) & 1) * KS * 32;
-            if (KS > 1) {
-                red[ks * 32 + threadIdx.x] = acc;
-                __syncthreads();
-                if (ks == 0) {
-                    acc = 0.f;
-                    for (int s = 0; s < KS; ++s) acc += red[s * 32 + threadIdx.x];
+        } else if (col_ok) {
+#pragma unroll
+            for (int t = 0; t < TT; ++t)
+                if (t < nt) {
+                    float acc = part[t];
+                    if (MODE == SCAN_SSD) acc = fmaf(skip, sV[t * 32 + threadIdx.x], acc);
+                    a.y[(size_t)(sg.row0 + t0 + t) * a.ldy + (size_t)h * dv + j] = acc;
                 }
-            }
-            if (ks == 0 && col_ok) {
-                if (MODE == SCAN_SSD) acc = fmaf(skip, v, acc);
-                a.y[(size_t)(sg.row0 + t0 + t) * a.ldy + (size_t)h * dv + j] = acc;
-            }
         }
     }
 #pragma unroll
@@ -193,19 +233,28 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
 }  // namespace
 
 int causal_conv_silu_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C,
-                         int taps, const SeqSeg* segs, int nseg, cudaStream_t st) {
+                         int taps, const SeqSeg* segs, int nseg, int max_n, cudaStream_t st) {
     B2_CHECK_ARG(in && w && bias && tail && out && segs && C > 0 && nseg > 0, "causal_conv: bad argument");
     B2_CHECK_ARG(taps >= 1 && taps <= CONV_MAX_TAPS, "causal_conv: 1..%d taps are supported (got %d)", CONV_MAX_TAPS, taps);
-    causal_conv_silu_kernel<<<dim3((C + 127) / 128, nseg), 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out, C, taps, segs);
+    // the grid covers the longest segment the call may hold; tiles past a segment's end return at once
+    causal_conv_silu_kernel<<<dim3((C + 127) / 128, (max_n + CONV_TILE - 1) / CONV_TILE, nseg), 128, 0, st>>>(in, ld_in, w, bias, tail, out, ld_out,
+                                                                                                             C, taps, segs);
     B2_LAUNCH_CHECK();
+    if (taps > 1) {
+        causal_conv_tail_kernel<<<dim3((C + 127) / 128, nseg), 128, 0, st>>>(in, ld_in, tail, C, taps, segs);
+        B2_LAUNCH_CHECK();
+    }
     return 0;
 }
 
 int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out, int64_t out_stride, int cols, int n_mix, const SeqSeg* segs,
-                        int nseg, cudaStream_t st) {
+                        int nseg, int max_n, cudaStream_t st) {
     B2_CHECK_ARG(x && mu && prev && out && segs && cols > 0 && nseg > 0, "token_shift: bad argument");
     B2_CHECK_ARG(n_mix >= 1 && n_mix <= SHIFT_MAX_MIX, "token_shift: 1..%d mixes are supported (got %d)", SHIFT_MAX_MIX, n_mix);
-    token_shift_mix_kernel<<<dim3((cols + 127) / 128, nseg), 128, 0, st>>>(x, mu, prev, out, out_stride, cols, n_mix, segs);
+    token_shift_mix_kernel<<<dim3((cols + 127) / 128, (max_n + SHIFT_TILE - 1) / SHIFT_TILE, nseg), 128, 0, st>>>(x, mu, prev, out, out_stride, cols,
+                                                                                                                 n_mix, segs);
+    B2_LAUNCH_CHECK();
+    token_shift_carry_kernel<<<dim3((cols + 127) / 128, nseg), 128, 0, st>>>(x, prev, cols, segs);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -215,7 +264,7 @@ int linear_scan_f32(const ScanArgs& a, cudaStream_t st) {
     B2_CHECK_ARG(a.heads > 0 && a.dk > 0 && a.dv > 0, "linear_scan: bad sizes");
     const int KS = (a.dk + KPT - 1) / KPT;
     B2_CHECK_ARG(KS <= 16, "linear_scan: key size %d exceeds %d", a.dk, 16 * KPT);
-    const size_t smem = ((size_t)3 * TT * KS * KPT + TT * 32 + 2 * KS * 32) * sizeof(float);
+    const size_t smem = ((size_t)3 * TT * KS * KPT + TT * 32 + (size_t)TT * KS * 32) * sizeof(float);
     dim3 grid((a.dv + 31) / 32, a.heads, a.nseg), block(32, KS);
     if (a.mode == SCAN_SSD) {
         B2_CHECK_ARG(a.groups > 0 && a.heads % a.groups == 0 && a.dt_bias && a.a_log && a.skip, "linear_scan(ssd): heads %d / groups %d", a.heads, a.groups);

@@ -143,13 +143,14 @@ struct Lin {  // one Linear call on the model's compute dtype
     }
 };
 
-int attn_nsplit(int rows, int H, int max_seq) {
-    // a decode step has few (row, head) warps: cut the keys so that the step fills the SMs (4 warps per CTA)
+int attn_nsplit(int rows, int G, int max_seq) {
+    // a decode step has few (row, key/value head) CTAs: cut the keys so that the step fills the SMs twice over, but keep
+    // at least 64 keys per cut at the cache's capacity
     if (rows > 8) return 1;
-    int n = (num_sms() * 4) / (rows * H);
-    const int cap = max_seq / 256;
+    int n = (2 * num_sms()) / (rows * G);
+    const int cap = max_seq / 64;
     if (n > cap) n = cap;
-    if (n > 32) n = 32;
+    if (n > 64) n = 64;
     return n < 1 ? 1 : n;
 }
 
@@ -167,6 +168,7 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
     float* x = s.x.as<float>();
     float* mix = s.mixout.as<float>();
     const SeqSeg* segs = s.segs.as<SeqSeg>();
+    const int max_n = nseg == 1 ? R : 1;  // a prompt portion is one segment of R rows; a decode step is R segments of one row
     for (size_t li = 0; li < s.layers.size(); ++li) {
         const SeqLayerInfo& L = s.layers[li];
         const b2_seq_layer_desc& d = L.d;
@@ -178,7 +180,7 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
             B2_TRY(lin(x, width, W.in_w, L.dproj, width, proj, L.dproj_ld, R));
             float* act = s.act.as<float>();  // [R, conv_ch] = silu(conv(x | B | C))
             B2_TRY(causal_conv_silu_f32(proj + L.inner, L.dproj_ld, W.conv_w.as<float>(), W.conv_b.as<float>(), S.conv_tail.as<float>(), act,
-                                        L.conv_ch, L.conv_ch, d.m_conv, segs, nseg, st));
+                                        L.conv_ch, L.conv_ch, d.m_conv, segs, nseg, max_n, st));
             ScanArgs sa;
             sa.mode = SCAN_SSD;
             sa.v = act; sa.ldv = L.conv_ch;
@@ -208,7 +210,8 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
             aa.H = d.a_heads; aa.G = d.a_kv_heads; aa.dk = d.a_dim; aa.dv = d.a_vdim; aa.Smax = kv->max_seq; aa.rows = R;
             aa.eps = eps; aa.scale = d.a_scale; aa.softcap = d.a_softcap; aa.temp_coef = d.a_temp_coef; aa.temp_every = d.a_temp_every;
             aa.row_slot = s.row_slot.as<int32_t>(); aa.row_pos = s.row_pos.as<int32_t>();
-            aa.nsplit = attn_nsplit(R, d.a_heads, kv->max_seq);
+            aa.nsplit = attn_nsplit(R, d.a_kv_heads, kv->max_seq);
+            aa.tile_rows = max_n;
             if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
             aa.partial = state.attn_partial.as<float>();
             B2_TRY(attn_prepare_f32(aa, st));
@@ -218,7 +221,7 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
             // ---- right: RWKV time mixing -------------------------------------------------------------------------------
             const size_t ms = (size_t)s.rows * width;  // stride between the five mixes (r, k, v, g, w)
             float* mixes = s.mixes.as<float>();
-            B2_TRY(token_shift_mix_f32(x, W.mu.as<float>(), S.prev.as<float>(), mixes, ms, width, 5, segs, nseg, st));
+            B2_TRY(token_shift_mix_f32(x, W.mu.as<float>(), S.prev.as<float>(), mixes, ms, width, 5, segs, nseg, max_n, st));
             float* rp = s.rp.as<float>();      // [4][rows][rn]: r, k, v, g
             const size_t rs = (size_t)s.rows * L.rn;
             B2_TRY(lin(mixes + 0 * ms, width, W.r_w, L.rn, width, rp + 0 * rs, L.rn, R));
@@ -486,7 +489,7 @@ int seq_kv_alloc(b2_kv* kv) {
             maxdv = std::max(maxdv, d.a_vdim);
         }
     }
-    kv->seq->nsplit_max = 32;
+    kv->seq->nsplit_max = 64;
     B2_TRY(kv->seq->attn_partial.alloc((size_t)8 * maxH * kv->seq->nsplit_max * (maxdv + 2) * F4));
     return 0;
 }
