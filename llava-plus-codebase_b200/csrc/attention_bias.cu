@@ -193,47 +193,73 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
         }
         for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)j0 * dv + e];
         __syncthreads();
+        // The warp's pairs go through the tile TOGETHER: a lane reads its key row once for all of them, and a value element
+        // once per key for all of them (shared-memory bandwidth, not the FMA pipe, limits this loop).
+        float sc[TL_PPW];
+#pragma unroll
+        for (int i = 0; i < TL_PPW; ++i) sc[i] = 0.f;
+        if (lane < nk) {
+            const float* kr = sK + lane * dkp;
+            if (VEC) {
+                for (int d = 0; d < dk; d += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kr + d);
+#pragma unroll
+                    for (int i = 0; i < TL_PPW; ++i) {
+                        if (ppos[i] >= j0) {           // idle pairs and pairs whose keys all lie ahead skip (warp-uniform)
+                            const float4 qv = *reinterpret_cast<const float4*>(sQ + (warp + TL_WARPS * i) * dk + d);
+                            sc[i] = fmaf(qv.x, kv.x, sc[i]); sc[i] = fmaf(qv.y, kv.y, sc[i]);
+                            sc[i] = fmaf(qv.z, kv.z, sc[i]); sc[i] = fmaf(qv.w, kv.w, sc[i]);
+                        }
+                    }
+                }
+            } else {
+                for (int d = 0; d < dk; ++d) {
+                    const float kv = kr[d];
+#pragma unroll
+                    for (int i = 0; i < TL_PPW; ++i)
+                        if (ppos[i] >= j0) sc[i] = fmaf(sQ[(warp + TL_WARPS * i) * dk + d], kv, sc[i]);
+                }
+            }
+        }
+        float pr[TL_PPW];
+        bool any = false;
 #pragma unroll
         for (int i = 0; i < TL_PPW; ++i) {
-            const int p = warp + TL_WARPS * i;
+            pr[i] = 0.f;
             const int pos = ppos[i];
-            if (pos < j0) continue;                    // idle pair, or every key of the tile is in its future (warp-uniform)
-            const int head = g * HG + p % HG;
+            if (pos < j0) continue;
+            any = true;
+            const int head = g * HG + (warp + TL_WARPS * i) % HG;
             const int j = j0 + lane;
             const bool valid = lane < nk && j <= pos;
-            float s = -INFINITY;
+            float sv = -INFINITY;
             if (valid) {
-                const float* q = sQ + p * dk;
-                const float* kr = sK + lane * dkp;
-                float acc = 0.f;
-                if (VEC) {
-                    for (int d = 0; d < dk; d += 4) {
-                        const float4 kv = *reinterpret_cast<const float4*>(kr + d);
-                        const float4 qv = *reinterpret_cast<const float4*>(q + d);
-                        acc = fmaf(qv.x, kv.x, acc); acc = fmaf(qv.y, kv.y, acc); acc = fmaf(qv.z, kv.z, acc); acc = fmaf(qv.w, kv.w, acc);
-                    }
-                } else {
-                    for (int d = 0; d < dk; ++d) acc = fmaf(q[d], kr[d], acc);
-                }
-                s = acc * a.scale;
-                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-                s += a.rel[(size_t)a.bucket_of[pos - j] * a.H + head];
+                sv = sc[i] * a.scale;
+                if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+                sv += a.rel[(size_t)a.bucket_of[pos - j] * a.H + head];
             }
-            const float m_new = fmaxf(m[i], warp_max(s));
-            const float pr = valid ? expf(s - m_new) : 0.f;
+            const float m_new = fmaxf(m[i], warp_max(sv));
+            pr[i] = valid ? expf(sv - m_new) : 0.f;
             const float corr = expf(m[i] - m_new);
-            l[i] = fmaf(l[i], corr, warp_sum(pr));
+            l[i] = fmaf(l[i], corr, warp_sum(pr[i]));
             m[i] = m_new;
 #pragma unroll
             for (int c = 0; c < AT_MAXC; ++c) o[i][c] *= corr;
-            const int nv = min(nk, pos - j0 + 1);
-            for (int jj = 0; jj < nv; ++jj) {
-                const float pj = __shfl_sync(0xffffffffu, pr, jj);
+        }
+        if (any) {
+            for (int jj = 0; jj < nk; ++jj) {
+                float pj[TL_PPW];
+#pragma unroll
+                for (int i = 0; i < TL_PPW; ++i) pj[i] = __shfl_sync(0xffffffffu, pr[i], jj);
                 const float* vr = sV + jj * dv;
 #pragma unroll
                 for (int c = 0; c < AT_MAXC; ++c) {
                     const int d = lane + 32 * c;
-                    if (d < dv) o[i][c] = fmaf(pj, vr[d], o[i][c]);
+                    if (d < dv) {
+                        const float vv = vr[d];
+#pragma unroll
+                        for (int i = 0; i < TL_PPW; ++i) o[i][c] = fmaf(pj[i], vv, o[i][c]);
+                    }
                 }
             }
         }
@@ -262,27 +288,43 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
     }
 }
 
-// one warp per (row, head): combines the key splits in split order
+// one warp per (row, head): combines the key splits in split order; lane s first turns split s's (max, sum) into its weight
 __global__ void attn_merge_kernel(BiasAttnArgs a) {
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= a.rows * a.H) return;
     const int r = w / a.H, h = w % a.H;
     if (a.row_pos[r] < 0) return;
     const float* part = a.partial + (size_t)w * a.nsplit * (a.dv + 2);
-    float m = -INFINITY;
-    for (int s = 0; s < a.nsplit; ++s) m = fmaxf(m, part[(size_t)s * (a.dv + 2)]);
-    float l = 0.f;
-    for (int s = 0; s < a.nsplit; ++s) {
-        const float* ps = part + (size_t)s * (a.dv + 2);
-        if (ps[1] > 0.f) l = fmaf(ps[1], expf(ps[0] - m), l);
-    }
-    for (int d = lane; d < a.dv; d += 32) {
-        float acc = 0.f;
-        for (int s = 0; s < a.nsplit; ++s) {
+    float mx = -INFINITY;
+    for (int s = lane; s < a.nsplit; s += 32) mx = fmaxf(mx, part[(size_t)s * (a.dv + 2)]);
+    mx = warp_max(mx);
+    float wgt[2] = {0.f, 0.f}, lsum = 0.f;   // nsplit <= 64: splits lane and lane + 32
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int s = lane + 32 * i;
+        if (s < a.nsplit) {
             const float* ps = part + (size_t)s * (a.dv + 2);
-            if (ps[1] > 0.f) acc = fmaf(ps[2 + d], expf(ps[0] - m), acc);
+            if (ps[1] > 0.f) { wgt[i] = expf(ps[0] - mx); lsum = fmaf(ps[1], wgt[i], lsum); }
         }
-        a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = acc / l;
+    }
+    const float inv = 1.f / warp_sum(lsum);
+    float acc[AT_MAXC];
+#pragma unroll
+    for (int c = 0; c < AT_MAXC; ++c) acc[c] = 0.f;
+    for (int s = 0; s < a.nsplit; ++s) {
+        const float ws = __shfl_sync(0xffffffffu, s < 32 ? wgt[0] : wgt[1], s & 31);
+        if (ws == 0.f) continue;
+        const float* ps = part + (size_t)s * (a.dv + 2) + 2;
+#pragma unroll
+        for (int c = 0; c < AT_MAXC; ++c) {
+            const int d = lane + 32 * c;
+            if (d < a.dv) acc[c] = fmaf(ps[d], ws, acc[c]);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < AT_MAXC; ++c) {
+        const int d = lane + 32 * c;
+        if (d < a.dv) a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = acc[c] * inv;
     }
 }
 
@@ -306,7 +348,7 @@ int attn_prepare_f32(const BiasAttnArgs& a, cudaStream_t st) {
 int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t st) {
     B2_TRY(check_args(a, "attn_bias"));
     B2_CHECK_ARG(a.out && a.rel && a.bucket_of, "attn_bias: null argument");
-    B2_CHECK_ARG(a.nsplit >= 1 && (a.nsplit == 1 || a.partial != nullptr), "attn_bias: key splits without scratch");
+    B2_CHECK_ARG(a.nsplit >= 1 && a.nsplit <= 64 && (a.nsplit == 1 || a.partial != nullptr), "attn_bias: 1..64 key splits, with scratch");
     const int warps = a.rows * a.H;
     const bool vec = a.dk % 4 == 0 && (reinterpret_cast<uintptr_t>(a.kcache) & 15) == 0;
     const int HG = a.H / a.G;

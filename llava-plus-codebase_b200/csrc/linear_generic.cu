@@ -43,9 +43,9 @@ __device__ __forceinline__ void ld_w8(const __nv_bfloat16* p, float (&w)[8]) {
     w[4] = __uint_as_float(t.z << 16); w[5] = __uint_as_float(t.z & 0xffff0000u);
     w[6] = __uint_as_float(t.w << 16); w[7] = __uint_as_float(t.w & 0xffff0000u);
 }
-// VEC kernel: a CTA of 8 warps takes 32 output columns (4 per warp, so a lane keeps 4 weight loads of 16 B in flight) and
+// VEC kernel: a CTA of 8 warps takes 16 output columns (2 per warp and two k-steps at a time, so a lane keeps 4 weight loads of 16 B in flight) and
 // stages the activation rows once in shared memory, KC columns at a time, already rounded to bf16 when the product is bf16.
-constexpr int RW_COLS = 4, RW_KC = 2048;
+constexpr int RW_COLS = 2, RW_KC = 2048;
 template <typename TW>
 __global__ void __launch_bounds__(256) linear_rows_vec_kernel(const float* __restrict__ A, int64_t lda, const TW* __restrict__ W, int64_t ldw,
                                                               const float* __restrict__ bias, float* __restrict__ out, int64_t ld_out, int M, int N,
@@ -68,23 +68,32 @@ __global__ void __launch_bounds__(256) linear_rows_vec_kernel(const float* __res
             *reinterpret_cast<float4*>(sA + e) = v;
         }
         __syncthreads();
-        for (int k = lane * 8; k < kc; k += 256) {
-            float wv[RW_COLS][8];
+        for (int k0 = lane * 8; k0 < kc; k0 += 512) {
+            // two k-steps x RW_COLS columns: 2 * RW_COLS weight loads of 16 B per lane are issued before the first is used
+            float wv[2][RW_COLS][8];
+            const bool second = k0 + 256 < kc;
 #pragma unroll
-            for (int c = 0; c < RW_COLS; ++c) {
-                // columns past N read the last row again: their sums are never stored
-                const int n = min(n0 + c, N - 1);
-                ld_w8(W + (size_t)n * ldw + kc0 + k, wv[c]);
-            }
+            for (int u = 0; u < 2; ++u)
 #pragma unroll
-            for (int m = 0; m < MR; ++m) {
-                if (m < M) {
-                    float av[8];
-                    ld_w8(sA + m * kc + k, av);
+                for (int c = 0; c < RW_COLS; ++c) {
+                    // columns past N read the last row again: their sums are never stored
+                    const int n = min(n0 + c, N - 1);
+                    if (u == 0 || second) ld_w8(W + (size_t)n * ldw + kc0 + k0 + u * 256, wv[u][c]);
+                }
 #pragma unroll
-                    for (int c = 0; c < RW_COLS; ++c)
+            for (int u = 0; u < 2; ++u) {
+                if (u == 0 || second) {
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[c][m] = fmaf(av[e], wv[c][e], acc[c][m]);
+                    for (int m = 0; m < MR; ++m) {
+                        if (m < M) {
+                            float av[8];
+                            ld_w8(sA + m * kc + k0 + u * 256, av);
+#pragma unroll
+                            for (int c = 0; c < RW_COLS; ++c)
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) acc[c][m] = fmaf(av[e], wv[u][c][e], acc[c][m]);
+                        }
+                    }
                 }
             }
         }
