@@ -43,23 +43,20 @@ __device__ __forceinline__ void ld_w8(const __nv_bfloat16* p, float (&w)[8]) {
     w[4] = __uint_as_float(t.z << 16); w[5] = __uint_as_float(t.z & 0xffff0000u);
     w[6] = __uint_as_float(t.w << 16); w[7] = __uint_as_float(t.w & 0xffff0000u);
 }
-// VEC kernel: a CTA of 8 warps takes 16 output columns (2 per warp and two k-steps at a time, so a lane keeps 4 weight loads of 16 B in flight) and
-// stages the activation rows once in shared memory, KC columns at a time, already rounded to bf16 when the product is bf16.
-constexpr int RW_COLS = 2, RW_KC = 2048;
+// VEC kernel: a CTA of 8 warps works on groups of 16 output columns (2 per warp and two k-steps at a time, so a lane keeps
+// 4 weight loads of 16 B in flight). The activation rows are staged in shared memory, already rounded to bf16 when the product
+// is bf16: whole (K <= kc_max) and then shared by every column group the CTA walks, or kc_max columns at a time for one group.
+constexpr int RW_COLS = 2, RW_SMEM_FLOATS = 16384;
 template <typename TW>
 __global__ void __launch_bounds__(256) linear_rows_vec_kernel(const float* __restrict__ A, int64_t lda, const TW* __restrict__ W, int64_t ldw,
                                                               const float* __restrict__ bias, float* __restrict__ out, int64_t ld_out, int M, int N,
-                                                              int K, int act, float alpha, int accumulate, int round_a) {
+                                                              int K, int kc_max, int act, float alpha, int accumulate, int round_a) {
     extern __shared__ float sA[];  // [M][kc]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = (blockIdx.x * 8 + warp) * RW_COLS;
-    float acc[RW_COLS][MR];
-#pragma unroll
-    for (int c = 0; c < RW_COLS; ++c)
-#pragma unroll
-        for (int m = 0; m < MR; ++m) acc[c][m] = 0.f;
-    for (int kc0 = 0; kc0 < K; kc0 += RW_KC) {
-        const int kc = min(RW_KC, K - kc0);
+    const int ngroups = (N + 8 * RW_COLS - 1) / (8 * RW_COLS);
+    const bool whole = K <= kc_max;      // otherwise gridDim.x == ngroups: one group per CTA, K in chunks
+    for (int kc0 = 0; kc0 < K; kc0 += kc_max) {
+        const int kc = min(kc_max, K - kc0);
         __syncthreads();
         for (int e = threadIdx.x * 4; e < M * kc; e += 1024) {
             const int m = e / kc, k = e % kc;
@@ -68,45 +65,57 @@ __global__ void __launch_bounds__(256) linear_rows_vec_kernel(const float* __res
             *reinterpret_cast<float4*>(sA + e) = v;
         }
         __syncthreads();
-        for (int k0 = lane * 8; k0 < kc; k0 += 512) {
-            // two k-steps x RW_COLS columns: 2 * RW_COLS weight loads of 16 B per lane are issued before the first is used
-            float wv[2][RW_COLS][8];
-            const bool second = k0 + 256 < kc;
+        for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x) {
+            const int n0 = (grp * 8 + warp) * RW_COLS;
+            float acc[RW_COLS][MR];
 #pragma unroll
-            for (int u = 0; u < 2; ++u)
+            for (int c = 0; c < RW_COLS; ++c)
 #pragma unroll
-                for (int c = 0; c < RW_COLS; ++c) {
-                    // columns past N read the last row again: their sums are never stored
-                    const int n = min(n0 + c, N - 1);
-                    if (u == 0 || second) ld_w8(W + (size_t)n * ldw + kc0 + k0 + u * 256, wv[u][c]);
-                }
+                for (int m = 0; m < MR; ++m) acc[c][m] = 0.f;
+            for (int k0 = lane * 8; k0 < kc; k0 += 512) {
+                // two k-steps x RW_COLS columns: 2 * RW_COLS weight loads of 16 B per lane are issued before the first is used
+                float wv[2][RW_COLS][8];
+                const bool second = k0 + 256 < kc;
 #pragma unroll
-            for (int u = 0; u < 2; ++u) {
-                if (u == 0 || second) {
+                for (int u = 0; u < 2; ++u)
 #pragma unroll
-                    for (int m = 0; m < MR; ++m) {
-                        if (m < M) {
-                            float av[8];
-                            ld_w8(sA + m * kc + k0 + u * 256, av);
+                    for (int c = 0; c < RW_COLS; ++c) {
+                        const int n = min(n0 + c, N - 1);  // columns past N read the last row again: their sums are never stored
+                        if (u == 0 || second) ld_w8(W + (size_t)n * ldw + kc0 + k0 + u * 256, wv[u][c]);
+                    }
 #pragma unroll
-                            for (int c = 0; c < RW_COLS; ++c)
+                for (int u = 0; u < 2; ++u) {
+                    if (u == 0 || second) {
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) acc[c][m] = fmaf(av[e], wv[u][c][e], acc[c][m]);
+                        for (int m = 0; m < MR; ++m) {
+                            if (m < M) {
+                                float av[8];
+                                ld_w8(sA + m * kc + k0 + u * 256, av);
+#pragma unroll
+                                for (int c = 0; c < RW_COLS; ++c)
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) acc[c][m] = fmaf(av[e], wv[u][c][e], acc[c][m]);
+                            }
                         }
                     }
                 }
             }
+#pragma unroll
+            for (int c = 0; c < RW_COLS; ++c)
+#pragma unroll
+                for (int m = 0; m < MR; ++m) {
+                    float v = acc[c][m];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    // K in chunks: the first chunk stores (or adds to what the caller asked to keep), later chunks add;
+                    // the activation is only legal on a whole K (checked on the host)
+                    if (lane == 0 && m < M && n0 + c < N) {
+                        if (whole) lin_store(out + (size_t)m * ld_out + n0 + c, v, bias, n0 + c, act, alpha, accumulate);
+                        else lin_store(out + (size_t)m * ld_out + n0 + c, v, kc0 == 0 ? bias : nullptr, n0 + c, LIN_NONE, alpha, accumulate || kc0 > 0);
+                    }
+                }
         }
     }
-#pragma unroll
-    for (int c = 0; c < RW_COLS; ++c)
-#pragma unroll
-        for (int m = 0; m < MR; ++m) {
-            float v = acc[c][m];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0 && m < M && n0 + c < N) lin_store(out + (size_t)m * ld_out + n0 + c, v, bias, n0 + c, act, alpha, accumulate);
-        }
 }
 
 // any K and alignment: one warp per output column, scalar loads
@@ -203,15 +212,25 @@ int launch_linear(const LinearArgs& a, cudaStream_t st) {
         const bool vec = a.K % 8 == 0 && a.lda % 4 == 0 && a.ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(a.W) & 15) == 0;
         if (vec) {
-            const size_t smem = (size_t)a.M * std::min(RW_KC, a.K) * sizeof(float);
             static bool attr_set = false;
             if (!attr_set) {
-                B2_CUDA_CHECK(cudaFuncSetAttribute(linear_rows_vec_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, MR * RW_KC * 4));
+                B2_CUDA_CHECK(cudaFuncSetAttribute(linear_rows_vec_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, RW_SMEM_FLOATS * 4));
                 attr_set = true;
             }
-            linear_rows_vec_kernel<TW><<<(a.N + 8 * RW_COLS - 1) / (8 * RW_COLS), 256, smem, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M,
-                                                                                                  a.N, a.K, a.act, a.alpha, a.accumulate, a.round_a);
-        } else {
+            int kc_max = RW_SMEM_FLOATS / a.M / 8 * 8;
+            // K in chunks accumulates through the output, which an activation forbids: such calls shrink nothing and take
+            // the whole K when it fits at all, else the scalar kernel
+            const int ngroups = (a.N + 8 * RW_COLS - 1) / (8 * RW_COLS);
+            if (a.K <= kc_max || a.act == LIN_NONE) {
+                const int grid = a.K <= kc_max ? std::min(ngroups, 3 * num_sms()) : ngroups;
+                const size_t smem = (size_t)a.M * std::min(kc_max, a.K) * sizeof(float);
+                linear_rows_vec_kernel<TW><<<grid, 256, smem, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M, a.N, a.K, kc_max, a.act,
+                                                                  a.alpha, a.accumulate, a.round_a);
+                B2_LAUNCH_CHECK();
+                return 0;
+            }
+        }
+        {
             linear_rows_kernel<TW><<<(a.N + 7) / 8, 256, 0, st>>>(a.A, a.lda, W, a.ldw, a.bias, a.out, a.ld_out, a.M, a.N, a.K, a.act, a.alpha,
                                                                  a.accumulate, a.round_a);
         }

@@ -152,31 +152,56 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
     float neg_a = 0.f, dtb = 0.f, skip = 0.f;
     if (MODE == SCAN_SSD) { neg_a = -expf(a.a_log[h]); dtb = a.dt_bias[h]; skip = a.skip[h]; }
 
+    // Staging is split in two so that global latency hides behind the walk of the previous tile: the raw inputs of tile
+    // i+1 are requested into registers before tile i is walked, and turned into (q, dt*k, decay, v) in shared memory after.
+    // A thread stages TT*KPT/32 key elements (dkp = KS*KPT over 32*KS threads) and up to TT value elements.
+    constexpr int EPT = TT * KPT / 32;
+    float rq[EPT], rk[EPT], rd[EPT], rv[TT];
+    auto fetch = [&](int t0) {
+        const int nt = min(TT, sg.n - t0);
+#pragma unroll
+        for (int u = 0; u < EPT; ++u) {
+            const int e = tid + u * nthr, t = e / dkp, key = e % dkp;
+            rq[u] = 0.f; rk[u] = 0.f; rd[u] = 0.f;
+            if (t < nt && key < dk) {
+                const size_t row = (size_t)(sg.row0 + t0 + t);
+                rq[u] = a.q[row * a.ldq + (size_t)g * dk + key];
+                rk[u] = a.k[row * a.ldk + (size_t)g * dk + key];
+                rd[u] = MODE == SCAN_SSD ? a.decay_in[row * a.ldd + h] : a.decay_in[row * a.ldd + (size_t)h * dk + key];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < TT; ++u) {
+            const int e = tid + u * nthr, t = e >> 5, jj = blockIdx.x * 32 + (e & 31);
+            rv[u] = (e < nt * 32 && jj < dv) ? a.v[(size_t)(sg.row0 + t0 + t) * a.ldv + (size_t)h * dv + jj] : 0.f;
+        }
+    };
+    fetch(0);
     for (int t0 = 0; t0 < sg.n; t0 += TT) {
         const int nt = min(TT, sg.n - t0);
         __syncthreads();
-        for (int e = tid; e < nt * dkp; e += nthr) {
-            const int t = e / dkp, key = e % dkp;
-            const size_t row = (size_t)(sg.row0 + t0 + t);
-            float q = 0.f, k = 0.f, d = 1.f;
+#pragma unroll
+        for (int u = 0; u < EPT; ++u) {
+            const int e = tid + u * nthr, key = e % dkp;
+            float k = rk[u], d = 1.f;
             if (key < dk) {
-                q = a.q[row * a.ldq + (size_t)g * dk + key];
-                k = a.k[row * a.ldk + (size_t)g * dk + key];
                 if (MODE == SCAN_SSD) {
-                    const float dt = softplus_f(a.decay_in[row * a.ldd + h] + dtb);
+                    const float dt = softplus_f(rd[u] + dtb);
                     d = expf(neg_a * dt);
                     k *= dt;
                 } else {
-                    d = expf(-expf(a.decay_in[row * a.ldd + (size_t)h * dk + key]));
+                    d = expf(-expf(rd[u]));
                 }
             }
-            sQ[e] = q; sK[e] = k; sD[e] = d;
+            sQ[e] = rq[u]; sK[e] = k; sD[e] = d;
         }
-        for (int e = tid; e < nt * 32; e += nthr) {
-            const int t = e >> 5, jj = blockIdx.x * 32 + (e & 31);
-            sV[e] = jj < dv ? a.v[(size_t)(sg.row0 + t0 + t) * a.ldv + (size_t)h * dv + jj] : 0.f;
+#pragma unroll
+        for (int u = 0; u < TT; ++u) {
+            const int e = tid + u * nthr;
+            if (e < TT * 32) sV[e] = rv[u];
         }
         __syncthreads();
+        if (t0 + TT < sg.n) fetch(t0 + TT);
         float part[TT];   // this thread's share of y[t][j] for the tokens of the tile
 #pragma unroll
         for (int t = 0; t < TT; ++t) {

@@ -117,6 +117,14 @@ bool tc_enabled() {  // B2_SEQ_TC=0: every Linear on the FMA kernels (A/B runs, 
     return !(e != nullptr && e[0] == '0');
 }
 
+int tc_min_rows() {  // fewest rows that take the tensor-core GEMM (below: the weight-streaming FMA kernels)
+    const char* e = getenv("B2_SEQ_TC_MIN_ROWS");
+    const int v = e != nullptr ? atoi(e) : 0;
+    // measured at widths 2048 / 4096 (decode step, ms): 4 rows 0.76 / 1.38 on the tile GEMM vs 0.78 / 1.48 on the FMA kernel,
+    // 8 rows 0.87 / 1.59 vs 1.14 / 3.45; 2 rows 0.71 / 1.28 vs 0.62 / 1.10
+    return v >= 1 ? v : 4;
+}
+
 struct Lin {  // one Linear call on the model's compute dtype
     const b2_model* m;
     cudaStream_t st;
@@ -131,7 +139,7 @@ struct Lin {  // one Linear call on the model's compute dtype
         // bf16 compute, a portion of a prompt: the tcgen05 GEMM on a bf16 copy of A (weights are stored with their rows
         // padded to a multiple of 8, zero-filled, so N rounds up; the pitch of every projection buffer is a multiple of 8)
         const int Np = (N + 7) / 8 * 8;
-        if (a.round_a && M >= 32 && N >= 32 && K % 8 == 0 && K >= 32 && K <= s.a16_w && ldo % 8 == 0 && Np <= ldo && bias == nullptr &&
+        if (a.round_a && M >= tc_min_rows() && N >= 32 && K % 8 == 0 && K >= 32 && K <= s.a16_w && ldo % 8 == 0 && Np <= ldo && bias == nullptr &&
             w_row0 == 0 && tc_enabled()) {
             B2_TRY(cast_rows_bf16(A, lda, s.a16.p, K, M, K, st));
             GemmArgs g;

@@ -160,16 +160,16 @@ def test_long_decoding_keeps_the_state(dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_batched_decode_of_unequal_requests_equals_each_alone(dtype):
     cfg = CFG_MAIN
-    model, w = build(cfg, dtype)
+    model, w = build(cfg, dtype, max_batch=6)
     eng = model._ensure_engine()
-    kv = eng.new_kv(4, 256)
-    reqs = [tokens_for(cfg, n, seed=10 + n) for n in (37, 14, 21)]
+    kv = eng.new_kv(6, 256)
+    reqs = [tokens_for(cfg, n, seed=10 + n) for n in (37, 14, 21, 50, 13)]    # five rows: the step's Linears take the tile GEMM in bf16
     steps = 12
-    alone = [run_schedule(eng, kv, 3, r, [len(r) - steps]) for r in reqs]      # slot 3, one request after the other
+    alone = [run_schedule(eng, kv, 5, r, [len(r) - steps]) for r in reqs]      # slot 5, one request after the other
     for b, r in enumerate(reqs):
         eng.append_tokens(kv, b, r[:len(r) - steps], [], restart=True)
     got = [[] for _ in reqs]
-    for s in range(steps):                                                    # one decode step over the three slots
+    for s in range(steps):                                                    # one decode step over the five slots
         col = torch.tensor([r[len(r) - steps + s] for r in reqs], dtype=torch.int32)
         lg = eng.decode_step(kv, col)
         for b in range(len(reqs)):
