@@ -200,7 +200,7 @@ enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2 };
 enum { B2_COMPUTE_BF16 = 0, B2_COMPUTE_F32 = 1 };
 typedef struct b2_seq_layer_desc {
     int32_t type;            /* B2_MIXER_* */
-    int32_t weights_of;      /* -1: own tensors; j < this layer: layer j's tensors, own state */
+    int32_t weights_of;      /* -1: own tensors; j: layer j's tensors (any other layer that owns its own), own state */
     int32_t ff;              /* feed-forward width (W_down relu(W_up x)^2); 0 = none */
     /* B2_MIXER_MAMBA2 */
     int32_t m_heads, m_vdim, m_state, m_groups, m_conv, m_norm_groups;

@@ -306,7 +306,7 @@ int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, f
 // ---- recurrent mixers (recurrent.cu) ----------------------------------------------------------------------------------
 // Causal depthwise convolution + SiLU with a carried tail: out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]);
 // inputs before the start of the call come from tail[slot][taps-1][C] (zeros when the segment starts a sequence); the tail is
-// replaced by the last taps-1 inputs. taps <= 8.
+// replaced by the last taps-1 inputs. taps <= 16.
 // max_n: the longest segment of the call (the launch grid covers that many rows per segment).
 int causal_conv_silu_f32(const float* in, int64_t ld_in, const float* w, const float* bias, float* tail, float* out, int64_t ld_out, int C,
                          int taps, const SeqSeg* segs, int nseg, int max_n, cudaStream_t stream);

@@ -16,7 +16,7 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 // One thread per (channel, tile of CONV_TILE tokens): it primes its window from the inputs in front of the tile (rows of this
 // call, or the carried tail for positions before the call) and walks the tile. The compute kernel only READS the tail; a
 // second small kernel replaces it afterwards, so tiles never race with the update.
-constexpr int CONV_MAX_TAPS = 8, CONV_TILE = 32;
+constexpr int CONV_MAX_TAPS = 16, CONV_TILE = 32;
 __global__ void __launch_bounds__(128) causal_conv_silu_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ w,
                                                                const float* __restrict__ bias, const float* __restrict__ tail,
                                                                float* __restrict__ out, int64_t ld_out, int C, int taps,

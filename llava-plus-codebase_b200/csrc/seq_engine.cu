@@ -535,17 +535,29 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
     s->rows = std::max(d.max_batch, d.max_rows);
     s->layers.resize(d.n_layers);
     s->w.resize(d.n_layers);
+    // a layer may name ANY other layer as the owner of its tensors (an owner that itself borrows is followed to its owner)
+    for (int i = 0; i < d.n_layers; ++i) s->layers[i].d = layers[i];
+    for (int i = 0; i < d.n_layers; ++i) {
+        int j = i, hops = 0;
+        while (j >= 0 && j < d.n_layers && s->layers[j].d.weights_of >= 0 && s->layers[j].d.weights_of != j && hops <= d.n_layers) {
+            j = s->layers[j].d.weights_of;
+            ++hops;
+        }
+        if (j < 0 || j >= d.n_layers || hops > d.n_layers) {
+            set_error("b2_seq_model_create: layer %d: weights_of does not lead to a layer that owns its tensors", i);
+            delete s;
+            return -1;
+        }
+        s->layers[i].src = j;
+    }
     for (int i = 0; i < d.n_layers; ++i) {
         SeqLayerInfo& L = s->layers[i];
-        L.d = layers[i];
         const b2_seq_layer_desc& l = L.d;
-        L.src = l.weights_of < 0 ? i : l.weights_of;
         const char* why = nullptr;
-        if (L.src > i || (L.src != i && s->layers[L.src].src != L.src)) why = "weights_of must name an earlier layer that owns its tensors";
-        else if (l.ff < 0) why = "negative feed-forward width";
+        if (l.ff < 0) why = "negative feed-forward width";
         else if (l.type == B2_MIXER_MAMBA2) {
             if (l.m_heads < 1 || l.m_vdim < 1 || l.m_state < 1 || l.m_groups < 1 || l.m_heads % l.m_groups) why = "mamba2: heads must be a positive multiple of groups";
-            else if (l.m_conv < 1 || l.m_conv > 8) why = "mamba2: 1..8 convolution taps";
+            else if (l.m_conv < 1 || l.m_conv > 16) why = "mamba2: 1..16 convolution taps";
             else if (l.m_norm_groups < 1 || (l.m_heads * l.m_vdim) % l.m_norm_groups) why = "mamba2: norm_groups must divide heads*vdim";
             else if (l.m_state > 256) why = "mamba2: state size above 256";
             L.inner = l.m_heads * l.m_vdim;
@@ -566,8 +578,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             why = "unknown mixer type";
         }
         if (why == nullptr && L.src != i) {
-            const b2_seq_layer_desc& o = s->layers[L.src].d;
-            b2_seq_layer_desc a = l, b = o;
+            b2_seq_layer_desc a = l, b = s->layers[L.src].d;
             a.weights_of = b.weights_of = -1;
             if (memcmp(&a, &b, sizeof(a)) != 0) why = "a layer that borrows weights must have the sizes of their owner";
         }

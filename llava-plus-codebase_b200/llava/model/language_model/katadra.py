@@ -60,8 +60,14 @@ class KatadraConfig:
             return cls(**json.load(f))
 
     def owner(self, i):
-        j = self.layers[i].get("weights_of")
-        return i if j is None else int(j)
+        """The layer whose tensors layer i computes with (itself, unless `weights_of` names another; chains are followed)."""
+        seen = set()
+        while self.layers[i].get("weights_of") is not None and int(self.layers[i]["weights_of"]) != i:
+            if i in seen:
+                raise ValueError(f"weights_of of layer {i} never reaches a layer that owns its tensors")
+            seen.add(i)
+            i = int(self.layers[i]["weights_of"])
+        return i
 
     def layer_descs(self, shapes):
         """Engine descriptions of the layers. Sizes the configuration does not spell out (rows of the distance-bias table, rank

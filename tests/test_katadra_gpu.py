@@ -36,7 +36,9 @@ def config(layers, width=96, vocab=160, eps=1e-5):
     return {"architecture": "Katadra", "width": width, "vocab": vocab, "norm": {"eps": eps}, "layers": copy.deepcopy(layers)}
 
 
+MAMBA5 = {"type": "mamba2", "mixer": {"heads": 4, "vdim": 8, "state": 36, "groups": 4, "conv": 5, "norm_groups": 2}, "mlp": None}
 CFG_MAIN = config([MAMBA, PAR, borrow(MAMBA, 0), borrow(PAR, 1)])
+CFG_FWD = config([borrow(MAMBA5, 2), PAR, MAMBA5], width=64)       # the first layer computes with the LAST layer's tensors
 CFG_ODD = config([PAR_ODD, MAMBA_ODD, MAMBA_ODD], width=90, vocab=77, eps=1e-3)
 
 
@@ -98,7 +100,7 @@ def test_each_mechanism_alone(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("cfg", [CFG_MAIN, CFG_ODD], ids=["main", "odd"])
+@pytest.mark.parametrize("cfg", [CFG_MAIN, CFG_ODD, CFG_FWD], ids=["main", "odd", "borrow_forward"])
 def test_whole_prompt_against_the_oracle(cfg, dtype):
     model, w = build(cfg, dtype)
     toks = tokens_for(cfg, 70)
