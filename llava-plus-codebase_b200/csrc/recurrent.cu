@@ -208,9 +208,16 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
             part[t] = 0.f;
             if (t < nt) {
                 const float v = sV[t * 32 + threadIdx.x];
-                const float* q = sQ + t * dkp + ks * KPT;
-                const float* k = sK + t * dkp + ks * KPT;
-                const float* d = sD + t * dkp + ks * KPT;
+                float q[KPT], k[KPT], d[KPT];   // this slice's 16 keys of the token: four 16-byte broadcast reads per array
+#pragma unroll
+                for (int i4 = 0; i4 < KPT / 4; ++i4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(sQ + t * dkp + ks * KPT + i4 * 4);
+                    const float4 k4 = *reinterpret_cast<const float4*>(sK + t * dkp + ks * KPT + i4 * 4);
+                    const float4 d4 = *reinterpret_cast<const float4*>(sD + t * dkp + ks * KPT + i4 * 4);
+                    q[i4 * 4] = q4.x; q[i4 * 4 + 1] = q4.y; q[i4 * 4 + 2] = q4.z; q[i4 * 4 + 3] = q4.w;
+                    k[i4 * 4] = k4.x; k[i4 * 4 + 1] = k4.y; k[i4 * 4 + 2] = k4.z; k[i4 * 4 + 3] = k4.w;
+                    d[i4 * 4] = d4.x; d[i4 * 4 + 1] = d4.y; d[i4 * 4 + 2] = d4.z; d[i4 * 4 + 3] = d4.w;
+                }
                 float acc = 0.f;
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) {
