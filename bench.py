@@ -14,7 +14,7 @@ e2e     : same metric through the public API model.generate(input_ids, images=..
           H2D of pixels + ids and D2H of the generated ids inside the timed region.
 roofline: the decode step (one launch of the persistent decode megakernel: all layers' weight-streaming GEMV
           phases + split-KV attention + lm_head + argmax), HBM-bound: algorithmic bytes/step = W + B*(Lc+1)*kv
-           over the measured step time, against MEASURED_PEAKS.json hbm_gbs.
+          over the measured step time, against MEASURED_PEAKS.json hbm_gbs.
 """
 import argparse
 import json
@@ -74,7 +74,7 @@ def peaks():
 def algorithmic_work(m, B, S, N, fp8=False):
     h, I, L = m["hidden"], m["inter"], m["layers"]
     layer_params = 4 * h * h + 3 * h * I
-    w_bytes = 2 * (L * (layer_params + 2 * h) + h + VOCAB * h)     # decode weight stream (bf16), SURVEY §8d
+    w_bytes = 2 * (L * (layer_params + 2 * h) + h + VOCAB * h)     # decode weight stream (bf16)
     if fp8:  # 1-byte Linear weights + one fp32 scale per output channel; norms stay bf16
         w_bytes = L * (layer_params + 4 * (5 * h + 2 * I) + 2 * 2 * h) + 2 * h + VOCAB * (h + 4)
     kv_per_tok = 2 * 2 * h * L                                     # K+V bf16, all layers, per token per sample
@@ -140,7 +140,7 @@ _CPU_WEIGHTS = {}
 
 
 CPU_THREADS = 16  # PyTorch's CPU GEMV/GEMM get SLOWER with every hardware thread of a many-core host (measured on this pool's
-                  # 128-thread hosts in round 1: 16 threads 13.1 tok/s, 64 threads 9.7, 128 threads 3.7): a fixed, stated count
+                  # 128-thread hosts: 16 threads 13.1 tok/s, 64 threads 9.7, 128 threads 3.7): a fixed, stated count
 
 
 _CPU_PIN = {}
@@ -648,7 +648,7 @@ def run_ours(args):
         e2e = e2e_stream = None
         if not args.no_e2e:
             def api_step():
-                # eos disabled (every run does exactly N steps; random-init logits can hit id 2 by chance)
+                # eos disabled
                 return model.generate(ids_host, images=images_host, do_sample=False, max_new_tokens=N, use_cache=True,
                                       eos_token_id=[])
             for _ in range(max(1, min(args.warmup, 2))):

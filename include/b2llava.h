@@ -4,7 +4,7 @@
  * class surface (llava/model/language_model/llava_llama.py:56-108, llava/model/llava_arch.py:94-240,
  * llava/model/multimodal_encoder/clip_encoder.py:39-51, llava/model/multimodal_projector/builder.py:33-51)
  * sitting directly on HuggingFace transformers + ATen. This header is the boundary we introduce where
- * HF/ATen sit today (SURVEY.md §8b): each entry point names the reference function whose arithmetic it
+ * HF/ATen sit today: each entry point names the reference function whose arithmetic it
  * replaces. The Python package `llava` in this repo binds it with ctypes.
  *
  * Conventions
@@ -77,7 +77,7 @@ int b2_version(void);
 unsigned long long b2_launch_count(void);/* number of kernels this library has launched (bench.py gpu_launches) */
 
 int b2_model_create(const b2_model_desc* desc, b2_model** out);
-/* Copy one checkpoint tensor into the model. `hf_key` uses the reference's state-dict names (SURVEY.md §5):
+/* Copy one checkpoint tensor into the model. `hf_key` uses the reference's state-dict names:
  * model.embed_tokens.weight, model.layers.{i}.self_attn.{q,k,v,o}_proj.weight,
  * model.layers.{i}.mlp.{gate,up,down}_proj.weight, model.layers.{i}.{input,post_attention}_layernorm.weight,
  * model.norm.weight, lm_head.weight, model.mm_projector.{0,2}.{weight,bias},
@@ -169,7 +169,7 @@ int b2_stream_begin(b2_model* m, b2_kv* kv, const float* logits, int B, const b2
 int b2_stream_enqueue(b2_model* m, b2_kv* kv, int n_steps, void* stream);
 int b2_stream_wait(b2_kv* kv, int index, int32_t* tokens_host, int timeout_ms);
 
-/* Continuous batching (SURVEY §8f-4: the reference's worker runs up to limit_model_concurrency generate() threads on one
+/* Continuous batching (the reference's worker runs up to limit_model_concurrency generate() threads on one
  * model, llava/serve/model_worker.py:230-243, each a batch-1 HF loop; here they share ONE batched decode step). The B slots of
  * a cache are a pool: b2_batch_begin puts the cache in per-slot mode (every slot idle, streaming ring armed);
  * b2_prefill_slots fills one slot; b2_batch_set_row(active=1) arms it with its own sampling parameters and the token chosen

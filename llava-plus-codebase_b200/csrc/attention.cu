@@ -2,8 +2,8 @@
 //   flash_attn_bf16  : prefill / ViT attention, flash-style online softmax, never materialises the
 //                      [B,H,S,S] score matrix the reference's eager path builds
 //                      (transformers modeling_llama.py:199-221 eager_attention_forward, modeling_clip.py:261-279).
-//                      bf16 operands, fp32 softmax statistics and accumulators. Round-1 implementation uses
-//                      mma.sync m16n8k16 (HMMA) tiles; it is <2% of prefill FLOPs (SURVEY §8a).
+//                      bf16 operands, fp32 softmax statistics and accumulators. This implementation uses
+//                      mma.sync m16n8k16 (HMMA) tiles; it is <2% of prefill FLOPs.
 //   rope_kv_write    : RoPE (modeling_llama.py:124-168, half-split rotate_half) on q,k of a prefill chunk and
 //                      the KV-cache write (modeling_llama.py:269-270 cache update).
 //   decode_attn_bf16 : one-token decode: RoPE + cache append + split-KV attention with coalesced 16-byte

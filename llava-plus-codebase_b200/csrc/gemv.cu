@@ -1,7 +1,7 @@
 // Weight-streaming GEMV for the one-token decode step outside the megakernel (batch 3..8, prefill's last-position
 // lm_head, B2_DECODE_MEGA=0):
 //     out[B, N] = (RMSNorm(x) | x)[B, K] · W[N, K]^T  (+ residual)      or the fused SwiGLU variant.
-// HBM-bound (SURVEY §3.4 / §8a a15-a18): every weight byte is read exactly once with 16-byte coalesced,
+// HBM-bound: every weight byte is read exactly once with 16-byte coalesced,
 // L1-bypassing loads from a persistent grid (one 512-thread CTA per SM, 16 loads in flight per lane through a
 // register double buffer; the first loads are issued BEFORE the activation prologue since weights do not depend
 // on the previous kernel's output).

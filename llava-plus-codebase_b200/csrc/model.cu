@@ -124,7 +124,7 @@ int skinny(b2_kv* kv, const void* x, int ldx, const void* W, int ldw, const void
 // Batch 7..128. Measured ladder (7B, ms/step, profiles/r1e_config_sweep_*.jsonl): the stream-K GEMM path costs 4.13-4.19 for
 // every B <= 8 (7 kernels/layer, ~8 us of fixed cost per GEMM launch: profiles/r1e_decode_launch_shares_b4.txt), the GEMV
 // path (5 kernels/layer, RMSNorm fused) 3.63 at B=4 and 4.51 at B=8 -> crossover between 6 and 7. B2_DECODE_SKINNY=0
-// restores the round-1 paths for A/B runs (GEMV kernels for B <= 8, tile GEMM with the batch padded to M=128 above),
+// restores the earlier paths for A/B runs (GEMV kernels for B <= 8, tile GEMM with the batch padded to M=128 above),
 // B2_DECODE_SKINNY=3 lowers the threshold to 3.
 // fp8 variant: xq8 / xscale hold the quantised activations of this GEMM
 int skinny8(b2_model* m, b2_kv* kv, const void* W8, const float* w_scale, const void* res, int ld_res, void* out, int ld_out,
@@ -192,7 +192,7 @@ int set_vision_weight(b2_model* m, const std::string& k, const void* ptr, const 
     if (k == "embeddings.position_ids") return 0;  // buffer in old checkpoints
     if (k == "pre_layrnorm.weight") { B2_TRY(expect_shape(key, shape, ndim, D)); return put(m->pre_g, D, 0, ptr, dt, D); }
     if (k == "pre_layrnorm.bias") { B2_TRY(expect_shape(key, shape, ndim, D)); return put(m->pre_b, D, 0, ptr, dt, D); }
-    if (starts_with(k, "post_layernorm.")) return 0;  // dead for select_layer=-2 (SURVEY App. B.4)
+    if (starts_with(k, "post_layernorm.")) return 0;  // dead for select_layer=-2
     if (starts_with(k, "encoder.layers.")) {
         int li = -1, consumed = 0;
         if (sscanf(key, "encoder.layers.%d.%n", &li, &consumed) != 1 || li < 0 || li >= m->d.vit_layers) {
@@ -459,7 +459,7 @@ int decode_step_launch(b2_model* m, b2_kv* kv, int B, cudaStream_t st) {
         B2_TRY(rmsnorm_bf16(m->x.p, h, m->final_norm.p, m->xn.p, B, h, d.rms_eps, st));
         B2_TRY(gemm(m->xn.p, h, m->lm_head.p, h, nullptr, nullptr, 0, m->logits.p, V, 1, B, V, h, ACT_NONE, st));
     }
-    {   // A/B switch for measurements: the round-1 tail (argmax + store_token + 2 x add_i32), greedy only, no host ring
+    {   // A/B switch for measurements: the four-launch tail (argmax + store_token + 2 x add_i32), greedy only, no host ring
         const char* e = getenv("B2_SAMPLE_LEGACY");
         if (e != nullptr && e[0] == '1' && kv->samp_host.do_sample == 0 && kv->samp_host.tag == 0 && kv->samp_host.per_row == 0) {
             B2_TRY(argmax_f32(m->logits.as<float>(), B, V, kv->tok.as<int32_t>(), st));

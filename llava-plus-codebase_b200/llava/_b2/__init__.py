@@ -165,7 +165,7 @@ def last_error():
 
 
 def check(rc, what=""):
-    """Error convention of the reference's callers (SURVEY §8b): ValueError for bad arguments,
+    """Error convention of the reference's callers: ValueError for bad arguments,
     RuntimeError for CUDA / state failures; never abort."""
     if rc == 0:
         return

@@ -1,7 +1,7 @@
-"""Continuous batching of concurrent generate() calls (SURVEY §8f-4).
+"""Continuous batching of concurrent generate() calls.
 
 The reference's worker serves concurrent requests by running up to `limit_model_concurrency` generate() THREADS on one
-model (/root/reference/llava/serve/model_worker.py:174-185, :230-243): each is a batch-1 HF loop and the GPU interleaves
+model (llava/serve/model_worker.py:174-185, :230-243): each is a batch-1 HF loop and the GPU interleaves
 them. A decode step at batch 1 and at batch 8 costs almost the same on this hardware (it streams the weights either way), so
 here those threads share ONE batched decode step instead: every thread still runs its own host loop (streamer, eos, stopping
 criteria — `_stream_decode` in llava_llama.py), but the tokens come from a scheduler that owns a KV cache with `slots` rows:

@@ -1,5 +1,5 @@
 """GPU image preprocessing for the LLaVA path — the device counterpart of the reference's `process_images`
-(/root/reference/llava/mm_utils.py:16-44): `expand2square` (when `image_aspect_ratio == 'pad'`) followed by
+(llava/mm_utils.py:16-44): `expand2square` (when `image_aspect_ratio == 'pad'`) followed by
 `CLIPImageProcessor.preprocess` as the reference's pinned transformers 4.31 runs it (PIL bicubic resize of the shortest
 edge, centre crop, rescale 1/255, normalise). Input: PIL images or uint8 HWC arrays of any size; output: `[n, 3, S, S]`
 bf16 on the device, ready for `encode_images`.

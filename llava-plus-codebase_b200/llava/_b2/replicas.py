@@ -1,4 +1,4 @@
-"""Data-parallel replicas (SURVEY §8e): the path shards by sample, one process per GPU, full weight replica per
+"""Data-parallel replicas: the path shards by sample, one process per GPU, full weight replica per
 GPU and NO collective on the hot path. The reference scales eval the same way (one process per GPU +
 get_chunk: llava/eval/model_vqa_loader.py:19-27, scripts/v1_5/eval/vqav2.sh:11-21) and merges results with
 `cat`. Here the only communication is the eval-harness gather of token ids / last-position logits and the

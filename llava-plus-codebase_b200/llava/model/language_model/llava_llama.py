@@ -2,7 +2,7 @@
 
 Same public surface as the reference's llava/model/language_model/llava_llama.py (LlavaConfig :29-30,
 LlavaLlamaModel :33-38, LlavaLlamaForCausalLM.forward :56-99, prepare_inputs_for_generation :101-108) and
-the same state-dict key layout (SURVEY.md §5), so `load_pretrained_model`, `llava.serve.model_worker`,
+the same state-dict key layout, so `load_pretrained_model`, `llava.serve.model_worker`,
 `llava.serve.cli` and the eval scripts can drive it unchanged. The modules here only HOLD checkpoint tensors;
 all arithmetic of the path (CLIP ViT, projector, splice, LLaMA prefill + KV-cache decode, lm_head, greedy
 argmax) runs in libb2llava.so through the C ABI in include/b2llava.h. There is no PyTorch fallback: without
@@ -370,7 +370,7 @@ class LlavaLlamaForCausalLM(nn.Module, LlavaMetaForCausalLM):
                  num_beams=1, max_new_tokens=None, max_length=None, use_cache=True, streamer=None,
                  stopping_criteria=None, eos_token_id=None, pad_token_id=None, attention_mask=None,
                  input_ids=None, output_scores=False, return_dict_in_generate=False, **kwargs):
-        """Own decoding loop with the side-protocols the reference's callers rely on (SURVEY §8b): prompt ids (with
+        """Own decoding loop with the side-protocols the reference's callers rely on: prompt ids (with
         IMAGE_TOKEN_INDEX) echoed in the result, `streamer.put/end`, `stopping_criteria` called as
         crit(ids_so_far, scores) -> bool | bool tensor, eos stop, temperature / top-k / top-p sampling.
 

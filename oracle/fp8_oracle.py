@@ -1,6 +1,6 @@
 """CPU restatement of the fp8 decode path (BASELINE.json configs[4]: "fp8-weight tcgen05 path") — TEST INFRASTRUCTURE ONLY.
 
-The reference has no fp8 path ("no reference exists for it at all; tolerance must be derived"), so this
+The reference has no fp8 path, so this
 file DEFINES the arithmetic the CUDA kernels implement and derives the tolerance against the bf16 oracle
 (oracle/llava_oracle.py, which restates llava/model/language_model/llava_llama.py:56-99 + HF modeling_llama.py):
 

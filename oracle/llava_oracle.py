@@ -3,8 +3,8 @@
 CPU restatement, in plain PyTorch, of the reference's multimodal forward path. Only `tests/`,
 `__graft_entry__.smoke()` and `bench.py`'s cpu_baseline / `--impl reference` legs may import this module.
 
-What it restates (reference = /root/reference @ a9f9d6fd; $HF = transformers 5.5.0, the version whose files
-were read; the reference pins 4.31.0 which implements the same math, SURVEY.md ยง8c):
+What it restates (reference = LLaVA-Plus-Codebase @ a9f9d6fd; $HF = transformers 5.5.0, the version whose files
+were read; the reference pins 4.31.0 which implements the same math):
 
   clip_vit_features     llava/model/multimodal_encoder/clip_encoder.py:29-51 (hidden_states[select_layer], drop CLS)
                         $HF/models/clip/modeling_clip.py:202-217 (embeddings), :261-279 + :300-336 (attention),
@@ -12,17 +12,17 @@ were read; the reference pins 4.31.0 which implements the same math, SURVEY.md ย
                         $HF/activations.py:122-123 (quick_gelu)
   mm_projector          llava/model/multimodal_projector/builder.py:39-46 (Linear -> GELU(erf) -> Linear)
   encode_images         llava/model/llava_arch.py:94-97
-  prepare_multimodal    llava/model/llava_arch.py:99-240 (splice semantics, probed in SURVEY App. C)
+  prepare_multimodal    llava/model/llava_arch.py:99-240 (splice semantics)
   llama_forward         $HF/models/llama/modeling_llama.py:62-67 (RMSNorm), :124-168 (RoPE), :182-184 (MLP),
                         :199-221 (eager attention), :251-289 (attention module), :303-332 (decoder layer),
                         :375-425 (model), :486-487 (lm_head); llava/model/language_model/llava_llama.py:56-99
-  greedy_generate       the manual greedy loop over the reference forward of SURVEY ยง8c (HF generate greedy search)
+  greedy_generate       the manual greedy loop over the reference forward (HF generate greedy search)
 
-Pinning: the reference ships NO tests or golden vectors for this path (SURVEY ยง4) โ "parity unpinned" by the
+Pinning: the reference ships NO tests or golden vectors for this path โ "parity unpinned" by the
 reference itself. This restatement is instead pinned against OUTPUTS OF THE UNMODIFIED REFERENCE FILES run in
 the build container (tests/golden/make_golden.py -> tests/golden/*.npz; checked by tests/test_oracle_golden.py).
 
-Weights are a flat dict keyed by the reference's state-dict names (SURVEY ยง5). `dtype=torch.float32` is the
+Weights are a flat dict keyed by the reference's state-dict names. `dtype=torch.float32` is the
 parity reference; `dtype=torch.bfloat16` reproduces the rounding points of the HF bf16 path (used for the CPU
 baseline timing and for the bf16-noise tolerance).
 """
@@ -119,7 +119,7 @@ def make_weights(cfg, seed=0, dtype=torch.float32):
 
 
 def condition_weights(w, cfg, seed=0, layer_gain=None):
-    """Well-conditioned variant of a weight set for STRICT greedy-id tests (SURVEY ยง7.3-2). Under plain random init the
+    """Well-conditioned variant of a weight set for STRICT greedy-id tests. Under plain random init the
     top-1/top-2 logit margin is of the order of the bf16 noise, so identical ids would be luck. Here the output head is
     tied to a permutation of the embedding table (lm_head[perm[t]] = embed_tokens[t]) and the residual branches
     (o_proj, down_proj) are damped by `layer_gain`, so the final hidden state keeps a cosine of ~0.3-0.5 with the embedding

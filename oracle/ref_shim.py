@@ -1,6 +1,6 @@
 """ORACLE SUPPORT — TEST INFRASTRUCTURE ONLY. Imports the UNMODIFIED reference hot-path files from
-/root/reference (build container only; the directory does not exist on the GPU box) on top of the installed
-transformers 5.5.0, following the recipe probed in SURVEY.md §8c / Appendix E:
+the reference checkout ($LLAVA_REFERENCE_ROOT; only the build container has one) on top of the installed
+transformers 5.5.0, following this recipe:
 
   (1) AutoConfig / AutoModelForCausalLM `register(..., exist_ok=True)` (llava_llama.py:110-111 collides with
       HF's built-in "llava" type),

@@ -2,7 +2,7 @@
 product; tests/ and __graft_entry__.smoke() are the only callers).
 
 What it restates: HF `GenerationMixin` token selection as the reference's callers invoke it
-(/root/reference/llava/serve/model_worker.py:155-185: do_sample = temperature > 0.001, temperature, top_p;
+(llava/serve/model_worker.py:155-185: do_sample = temperature > 0.001, temperature, top_p;
 llava/eval/model_vqa_loader.py:98-106: greedy when temperature == 0). The arithmetic lives in the third-party
 `transformers` package (reference pins 4.31.0, pyproject.toml:17; installed here: 5.5.0):
   TemperatureLogitsWarper  scores / temperature

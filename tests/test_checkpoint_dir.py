@@ -1,7 +1,7 @@
-"""Real-checkpoint ingestion (VERDICT r1 missing #5 / row f3): a synthetic HF-format `llava` checkpoint
+"""Real-checkpoint ingestion: a synthetic HF-format `llava` checkpoint
 directory — config.json whose `mm_vision_tower` is a HUB ID, SHARDED safetensors + index, a sentencepiece
 tokenizer.model — goes through the reference's loader contract `load_pretrained_model(model_path, None, model_name)`
-(/root/reference/llava/model/builder.py:26-151) and generates; the tower resolves through the local HuggingFace cache like
+(llava/model/builder.py:26-151) and generates; the tower resolves through the local HuggingFace cache like
 the reference's `from_pretrained(vision_tower_name)` (llava/model/multimodal_encoder/clip_encoder.py:22-27).
 
 CPU part: directory layout, shard reading, hub-id resolution, failure modes. GPU part: load -> generate equals a model
@@ -60,7 +60,7 @@ def write_tokenizer(path, vocab_size):
 
 
 def write_llava_checkpoint(path, cfg, weights, shards=3):
-    """llava-v1.5-style directory: LlavaConfig fields the reference persists (SURVEY §5), fp16 tensors in `shards` files."""
+    """llava-v1.5-style directory: LlavaConfig fields the reference persists, fp16 tensors in `shards` files."""
     from safetensors.torch import save_file
 
     os.makedirs(path, exist_ok=True)

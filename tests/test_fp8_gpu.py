@@ -1,5 +1,5 @@
-"""GPU: the fp8 decode path (BASELINE configs[4]) against oracle/fp8_oracle.py, through the C ABI (first executed on a
-B200 in round 2: profiles/r2a_fp8_2cta_first_run.txt)."""
+"""GPU: the fp8 decode path (BASELINE configs[4]) against oracle/fp8_oracle.py, through the C ABI (first run on a B200:
+profiles/r2a_fp8_2cta_first_run.txt)."""
 import pytest
 import torch
 

@@ -1,4 +1,4 @@
-"""GPU: FULL-DEPTH parity at the BASELINE configs (VERDICT r1 weak #1): the 32-layer LLaVA-1.5-7B stack on configs[1]'s
+"""GPU: FULL-DEPTH parity at the BASELINE configs: the 32-layer LLaVA-1.5-7B stack on configs[1]'s
 inputs (one 336 px image + 128 text tokens, S = 704) and the 40-layer 13B stack, engine (bf16, fp32 accumulation) against
 the fp32 oracle on the host cores: vision features, last-position prefill logits and 16 teacher-forced decode steps, with
 the measured errors written to gpurun_out/full_depth_parity.json; plus STRICT greedy-id equality on the well-conditioned

@@ -209,7 +209,7 @@ def test_generate_from_a_worker_thread_with_iterator_streamer_and_keyword_stop()
 
 
 def test_concurrent_generate_threads_do_not_share_a_cache():
-    """ADVICE r1 (high): two requests in flight on one model must not see each other's context."""
+    """two requests in flight on one model must not see each other's context."""
     cfg, model = _tiny_model()
     prompts = [synth_inputs(cfg, B=1, Lt=10 + 3 * i, seed=20 + i) for i in range(4)]
     serial = [model.generate(p.to(DEV), images=im.to(DEV), do_sample=False, max_new_tokens=24, eos_token_id=[]).cpu()
@@ -248,7 +248,7 @@ def test_forward_caches_are_leases():
 
 
 def test_bad_ids_raise_instead_of_reading_out_of_bounds():
-    """ADVICE r1 (medium): ids >= vocab / a leftover image placeholder must not fault the context."""
+    """ids >= vocab / a leftover image placeholder must not fault the context."""
     cfg, model = _tiny_model()
     ids, images = synth_inputs(cfg, B=1, Lt=10, seed=1)
     bad = ids.clone()
@@ -323,7 +323,7 @@ def test_generate_with_device_ids_falls_back_to_reference_semantics_on_odd_input
 
 # ------------------------------------------------------------------------------------------------ continuous batching
 def test_continuous_batching_of_concurrent_generate_threads():
-    """six worker threads call generate() on ONE model (the reference worker's pattern, model_worker.py:174-185,
+    """Six worker threads call generate() on ONE model (the reference worker's pattern, model_worker.py:174-185,
     230-243); with config.b2_continuous_batching = 4 their decode steps are shared. On the well-conditioned weight set every
     request must produce exactly the ids it produces alone on an unbatched model — requests join and leave the batch at
     different steps (different prompt lengths, max_new_tokens, one keyword stop, one sampled request)."""

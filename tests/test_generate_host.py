@@ -1,6 +1,6 @@
 """CPU: host-side logic of generate()'s decode loop (`_stream_decode`: run-ahead scheduling over the streaming C-ABI, eos /
 pad bookkeeping, streamer and stopping-criteria protocol) against a plain per-step restatement of the loop the reference's
-callers get from HF generate (SURVEY §8b): finished rows show the pad id, generation stops at the step where every row
+callers get from HF generate: finished rows show the pad id, generation stops at the step where every row
 has finished or a criterion fires, the result never exceeds max_new_tokens, the device is never asked for more steps than
 max_new_tokens - 1 and never runs more than `run_ahead` tokens in front of the host."""
 import torch
@@ -123,7 +123,7 @@ def test_tensor_valued_criteria_are_accepted():
 
 def test_kv_pool_hands_out_exclusive_caches_and_blocks_at_its_cap():
     """_KVPool (one cache per generate() call): caches are created on demand up to `cap`, reused after release, and a
-    third concurrent acquire waits for a release instead of sharing a cache (per-generate KV cache)."""
+    third concurrent acquire waits for a release instead of sharing a cache."""
     import threading
     import time
     from llava.model.language_model.llava_llama import _KVPool

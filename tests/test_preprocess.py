@@ -1,4 +1,4 @@
-"""Image preprocessing on the device (VERDICT r1 missing #3): csrc/preprocess.cu + llava/_b2/preprocess.py against
+"""Image preprocessing on the device: csrc/preprocess.cu + llava/_b2/preprocess.py against
 the reference's arithmetic — `expand2square` (llava/mm_utils.py:16-27) and PIL's bicubic resize, which is what
 CLIPImageProcessor.preprocess runs under the reference's pinned transformers 4.31. The 8-bit resized image must equal PIL's
 BIT FOR BIT; the normalised bf16 output must be the bf16 rounding of the fp32 pipeline; the INSTALLED transformers 5.5

@@ -58,7 +58,7 @@ def test_grouped_images_flatten_into_one_slot():
 
 def test_missing_image_slot_raises_like_reference():
     ids = np.array([[1, 5, 6, 7], [1, O.IMAGE_TOKEN_INDEX, 5, 6]], dtype=np.int64)
-    with pytest.raises(IndexError):  # row 0 consumes the only slot (SURVEY App. C.2)
+    with pytest.raises(IndexError):  # row 0 consumes the only slot
         build_source_index(ids, np.ones_like(ids, bool), np.full_like(ids, -100), 16, [16], None, "right")
 
 
@@ -83,7 +83,7 @@ def _random_case(rng, B, P, n_feat_rows_per_slot):
         k = int(rng.integers(0, 4))
         where = rng.choice(n, size=min(k, n), replace=False)
         ids[b, where] = O.IMAGE_TOKEN_INDEX
-        slots += max(len(where), 1)  # a row without <image> still consumes one slot (SURVEY App. C.2)
+        slots += max(len(where), 1)  # a row without <image> still consumes one slot
     labels = rng.integers(0, 90, size=(B, Lt)).astype(np.int64)
     feats = [rng.standard_normal((n_feat_rows_per_slot, 8)).astype(np.float32) for _ in range(slots)]
     return ids, mask, labels, feats

@@ -1,4 +1,4 @@
-"""CPU: the reference-facing class surface (SURVEY §8b) that can be checked without a GPU — factories, error behaviour,
+"""CPU: the reference-facing class surface that can be checked without a GPU — factories, error behaviour,
 state-dict key layout, tower properties — so that `llava/model/builder.py`-style callers find what they expect. Anything
 that would compute must raise (there is no CPU path)."""
 import types
@@ -54,8 +54,7 @@ def test_build_vision_projector_contract():
 
 
 def test_state_dict_layout_and_tower_properties(model):
-    """The checkpoint key layout of the reference (oracle.weight_shapes is asserted against the unmodified
-    reference's own state_dict in oracle/ref_shim.py) and the CLIPVisionTower properties model_worker / builder.py read."""
+    """The checkpoint key layout of the reference and the CLIPVisionTower properties model_worker / builder.py read."""
     cfg, m = model
     vt = m.get_vision_tower()
     assert vt is m.get_model().get_vision_tower() and not vt.is_loaded
