@@ -157,8 +157,10 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
     // A thread stages TT*KPT/32 key elements (dkp = KS*KPT over 32*KS threads) and up to TT value elements.
     constexpr int EPT = TT * KPT / 32;
     float rq[EPT], rk[EPT], rd[EPT], rv[TT];
+    float rtok = 0.f;  // SSD: the raw step size of token `tid` of the tile (one scalar per token and head)
     auto fetch = [&](int t0) {
         const int nt = min(TT, sg.n - t0);
+        if (MODE == SCAN_SSD && tid < nt) rtok = a.decay_in[(size_t)(sg.row0 + t0 + tid) * a.ldd + h];
 #pragma unroll
         for (int u = 0; u < EPT; ++u) {
             const int e = tid + u * nthr, t = e / dkp, key = e % dkp;
@@ -167,7 +169,7 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
                 const size_t row = (size_t)(sg.row0 + t0 + t);
                 rq[u] = a.q[row * a.ldq + (size_t)g * dk + key];
                 rk[u] = a.k[row * a.ldk + (size_t)g * dk + key];
-                rd[u] = MODE == SCAN_SSD ? a.decay_in[row * a.ldd + h] : a.decay_in[row * a.ldd + (size_t)h * dk + key];
+                if (MODE == SCAN_RWKV) rd[u] = a.decay_in[row * a.ldd + (size_t)h * dk + key];
             }
         }
 #pragma unroll
@@ -183,17 +185,15 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int u = 0; u < EPT; ++u) {
             const int e = tid + u * nthr, key = e % dkp;
-            float k = rk[u], d = 1.f;
-            if (key < dk) {
-                if (MODE == SCAN_SSD) {
-                    const float dt = softplus_f(rd[u] + dtb);
-                    d = expf(neg_a * dt);
-                    k *= dt;
-                } else {
-                    d = expf(-expf(rd[u]));
-                }
-            }
-            sQ[e] = rq[u]; sK[e] = k; sD[e] = d;
+            sQ[e] = rq[u]; sK[e] = rk[u];
+            if (MODE == SCAN_RWKV) sD[e] = key < dk ? expf(-expf(rd[u])) : 1.f;
+        }
+        // SSD: the decay and the step size are scalars per token; the step size multiplies the value (dt B x^T = B (dt x)^T),
+        // so the keys are staged as they are and sD holds [TT] step sizes followed by [TT] decays
+        if (MODE == SCAN_SSD && tid < TT) {
+            const float dt = softplus_f(rtok + dtb);
+            sD[tid] = dt;
+            sD[TT + tid] = expf(neg_a * dt);
         }
 #pragma unroll
         for (int u = 0; u < TT; ++u) {
@@ -213,20 +213,23 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
                 for (int i4 = 0; i4 < KPT / 4; ++i4) {
                     const float4 q4 = *reinterpret_cast<const float4*>(sQ + t * dkp + ks * KPT + i4 * 4);
                     const float4 k4 = *reinterpret_cast<const float4*>(sK + t * dkp + ks * KPT + i4 * 4);
-                    const float4 d4 = *reinterpret_cast<const float4*>(sD + t * dkp + ks * KPT + i4 * 4);
                     q[i4 * 4] = q4.x; q[i4 * 4 + 1] = q4.y; q[i4 * 4 + 2] = q4.z; q[i4 * 4 + 3] = q4.w;
                     k[i4 * 4] = k4.x; k[i4 * 4 + 1] = k4.y; k[i4 * 4 + 2] = k4.z; k[i4 * 4 + 3] = k4.w;
-                    d[i4 * 4] = d4.x; d[i4 * 4 + 1] = d4.y; d[i4 * 4 + 2] = d4.z; d[i4 * 4 + 3] = d4.w;
+                    if (MODE == SCAN_RWKV) {
+                        const float4 d4 = *reinterpret_cast<const float4*>(sD + t * dkp + ks * KPT + i4 * 4);
+                        d[i4 * 4] = d4.x; d[i4 * 4 + 1] = d4.y; d[i4 * 4 + 2] = d4.z; d[i4 * 4 + 3] = d4.w;
+                    }
                 }
                 float acc = 0.f;
+                const float vdt = MODE == SCAN_SSD ? v * sD[t] : v, dec = MODE == SCAN_SSD ? sD[TT + t] : 0.f;
 #pragma unroll
                 for (int i = 0; i < KPT; ++i) {
-                    const float kv = k[i] * v;
+                    const float kv = k[i] * vdt;
                     if (MODE == SCAN_RWKV) {
                         acc = fmaf(q[i], fmaf(bon[i], kv, S[i]), acc);
                         S[i] = fmaf(d[i], S[i], kv);
                     } else {
-                        S[i] = fmaf(d[i], S[i], kv);
+                        S[i] = fmaf(dec, S[i], kv);
                         acc = fmaf(q[i], S[i], acc);
                     }
                 }
