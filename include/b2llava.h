@@ -190,18 +190,34 @@ int b2_batch_set_row(b2_model* m, b2_kv* kv, int slot, int active, const b2_samp
  *                      rotation (unit-RMS q and k, logarithmic query temperature, tanh soft-cap, bucketed distance bias,
  *                      grouped key/value heads, sigmoid output gate); the RWKV side has token-shift mixes, a low-rank
  *                      per-channel decay, a bonus for the current token, per-head unit-RMS norm and a SiLU gate
+ *   B2_MIXER_LATENT_ATTN  attention without positions over a low-rank latent: q = W_q h; the cached row of a token is
+ *                      c = unit_rms(W_dkv h) * g; per head k = W_uk c, v = W_uv c (computed in the absorbed form: the query
+ *                      is carried into the latent space, the latent-space output is carried out by W_uv, so only c is
+ *                      cached); softmax with a per-head sink term in the denominator; per-head sigmoid output gate
+ *   B2_MIXER_HGRN2     gated linear recurrence S <- diag(f) S + (1 - f) v^T, o = S^T silu(W_q h), with the forget gate
+ *                      f = l + (1 - l) sigmoid(W_f h + b) bounded below by a learned l; per-head unit-RMS norm
+ * Blocks: B2_BLOCK_POST_LN adds the LayerNorm of every sublayer's OUTPUT; B2_BLOCK_PRE_RMS1 is pre-norm,
+ * x += residual_mult * sublayer(g * unit_rms(x)) with ONE learned number g per norm (also in front of the head).
+ * Feed-forwards: B2_FF_RELU_SQ (W_down relu(W_up x)^2), B2_FF_POLYNORM (biased projections around
+ * a N(z) + b N(z^2) + c N(z^3) + e, N = division by the token's root mean square), B2_FF_MOE (sigmoid router, group-limited
+ * top-k, SiLU-gated experts without biases, optional shared expert).
+ * A model may add a hashed bigram row to every token embedding, loop a block of layers several times with the same tensors
+ * (every pass has its own cache/state; before a pass the embedding output is added again from the second pass on, and a
+ * learned per-pass vector always), and soft-cap its logits with tanh.
  * The reference has no such models (its LLMs are HF LLaMA / MPT, llava/model/language_model/); what is shared with the
  * LLaVA path is everything around the layers: b2_kv slots and lengths, b2_decode_step / b2_decode_greedy / b2_stream_* /
  * b2_batch_* (CUDA-graph decode step, device-side token selection, host token ring, continuous batching).
  * compute: B2_COMPUTE_BF16 = bf16 x bf16 -> fp32 matrix products on bf16 weights, everything else fp32;
  *          B2_COMPUTE_F32  = true fp32 throughout (weights widened at load, FMA products, no TF32). */
 enum { B2_ARCH_LLAVA = 0, B2_ARCH_LAYER_LIST = 1 };
-enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2 };
+enum { B2_MIXER_MAMBA2 = 1, B2_MIXER_PARALLEL = 2, B2_MIXER_LATENT_ATTN = 3, B2_MIXER_HGRN2 = 4 };
+enum { B2_FF_RELU_SQ = 0, B2_FF_POLYNORM = 1, B2_FF_MOE = 2 };
+enum { B2_BLOCK_POST_LN = 0, B2_BLOCK_PRE_RMS1 = 1 };
 enum { B2_COMPUTE_BF16 = 0, B2_COMPUTE_F32 = 1 };
 typedef struct b2_seq_layer_desc {
     int32_t type;            /* B2_MIXER_* */
     int32_t weights_of;      /* -1: own tensors; j: layer j's tensors (any other layer that owns its own), own state */
-    int32_t ff;              /* feed-forward width (W_down relu(W_up x)^2); 0 = none */
+    int32_t ff;              /* feed-forward width (of one expert for B2_FF_MOE); 0 = none */
     /* B2_MIXER_MAMBA2 */
     int32_t m_heads, m_vdim, m_state, m_groups, m_conv, m_norm_groups;
     /* B2_MIXER_PARALLEL, attention side */
@@ -210,6 +226,16 @@ typedef struct b2_seq_layer_desc {
     /* B2_MIXER_PARALLEL, RWKV side */
     int32_t r_heads, r_dim, r_decay_rank;
     float left_scale, right_scale;
+    /* feed-forward */
+    int32_t ff_kind;         /* B2_FF_* */
+    int32_t moe_experts, moe_top, moe_groups, moe_keep;   /* B2_FF_MOE: experts, choices per token, groups of neighbours, groups kept */
+    int32_t moe_shared_ff;   /* width of the shared expert; 0 = none */
+    float moe_scale;         /* factor on the normalised weights of the chosen experts */
+    /* B2_MIXER_LATENT_ATTN */
+    int32_t la_heads, la_dim, la_vdim, la_rank;
+    float la_scale;
+    /* B2_MIXER_HGRN2 */
+    int32_t g_heads, g_dim, g_vdim;
 } b2_seq_layer_desc;
 typedef struct b2_seq_model_desc {
     int32_t width, vocab, n_layers;
@@ -217,16 +243,27 @@ typedef struct b2_seq_model_desc {
     float norm_eps;
     int32_t max_batch;       /* slots a cache of this model may have (rows of a decode step) */
     int32_t max_rows;        /* most tokens one b2_append_tokens call brings */
+    int32_t block;           /* B2_BLOCK_* */
+    float residual_mult;     /* B2_BLOCK_PRE_RMS1: factor on every sublayer's output */
+    float logit_softcap;     /* logits <- cap * tanh(logits / cap); 0 = none */
+    int32_t bigram_buckets, bigram_mul_prev, bigram_mul_cur;  /* hashed bigram embedding: row (prev * mul_prev + cur * mul_cur) mod
+                                                                 buckets, row `buckets` for a sequence's first token; 0 buckets = none */
+    int32_t loop_start, loop_stop, loop_times;                /* layers [start, stop) run `times` times in a row; times <= 1: no loop */
 } b2_seq_model_desc;
 int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* layers, b2_model** out);
+/* Layer RUNS of one forward pass (a looped layer counts every time): rows of b2_append_tokens' resid_out; -1 for other models */
+int b2_seq_model_runs(const b2_model* m);
 /* Tensor names for b2_model_set_weight on such a model: embed, head, final.norm[.b], l<i>.norm1[.b], l<i>.norm2[.b],
  * l<i>.mix.{in,conv,conv.b,dt_bias,A_log,D,norm,o}, l<i>.mix.left.{q,k,v,g,rel,o}, l<i>.mix.right.{mu.r,mu.k,mu.v,mu.g,mu.w,
- * r,k,v,g,w1,w2,w0,u,norm,o}, l<i>.mlp.{up,down}; Linear weights are [out, in]. */
+ * r,k,v,g,w1,w2,w0,u,norm,o}, l<i>.mlp.{up,down}; Linear weights are [out, in].
+ * B2_BLOCK_PRE_RMS1 models: embed, bigram, loop.step, head, final.norm, l<i>.norm1, l<i>.norm2 (one number each),
+ * l<i>.mix.{q,dkv,dkv.norm,uk,uv,sink,g,o} (latent attention), l<i>.mix.{q,f,f.b,lower,v,norm,o} (HGRN2),
+ * l<i>.mlp.{up,up.b,down,down.b,act} (PolyNorm), l<i>.mlp.{router,e<j>.gate,e<j>.up,e<j>.down,shared.gate,shared.up,shared.down}. */
 /* Feed the next n tokens of the request in cache slot `slot` (a portion of its prompt, or all of it): the slot's state and
  * key/value rows continue from its current length, or from an empty sequence when restart != 0 (whatever the slot held
  * is then dead: nothing needs clearing). want_host lists n_want indices into these n tokens whose logits are written to
- * logits_out (device or host fp32 [n_want, vocab]); resid_out (device fp32 [n_layers, n, width], nullable) receives the
- * residual stream after every layer. The logits do not depend on how a prompt is cut into calls, beyond rounding. */
+ * logits_out (device or host fp32 [n_want, vocab]); resid_out (device fp32 [layer runs, n, width], nullable) receives the
+ * residual stream after every layer run. The logits do not depend on how a prompt is cut into calls, beyond rounding. */
 int b2_append_tokens(b2_model* m, b2_kv* kv, int slot, const int32_t* tokens_host, int n, int restart, const int32_t* want_host,
                      int n_want, float* logits_out, float* resid_out, void* stream);
 /* b2_decode_step over the slots [slot0, slot0 + B) (b2_decode_step == slot0 0); layer-list models only for slot0 > 0 */

@@ -5,6 +5,9 @@
 // share key/value heads in groups; key and value sizes are free (dk, dv <= 256). Everything is fp32: scores, softmax,
 // the cache. One warp per (row, head [, key split]); a row is a token of a prompt portion or a decode step, and it attends
 // to its slot's cache, which attn_prepare has already extended by the rows of this call.
+// The same kernels serve attention over a shared latent (one cached row per token that is key AND value of every head:
+// kcache == vcache, dk == dv <= 512, G = 1), without bias table or soft-cap (rel == null), and with a per-head sink: one
+// extra term exp(sink[h]) in the softmax denominator that has no key and no value.
 #include <math.h>
 
 #include "common.cuh"
@@ -100,7 +103,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
             }
             s = acc * a.scale;
             if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-            s += a.rel[(size_t)a.bucket_of[pos - j] * a.H + h];
+            if (a.rel != nullptr) s += a.rel[(size_t)a.bucket_of[pos - j] * a.H + h];
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -129,7 +132,11 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
             if (d < a.dv) part[2 + d] = o[c];
         }
     } else {
-        const float inv = 1.f / l;
+        float inv = 1.f / l;
+        if (a.sink != nullptr) {   // the sink joins the denominator once, under the common maximum
+            const float sk = a.sink[h], mf = fmaxf(m, sk), c0 = expf(m - mf);
+            inv = c0 / fmaf(l, c0, expf(sk - mf));
+        }
 #pragma unroll
         for (int c = 0; c < AT_MAXC; ++c) {
             const int d = lane + 32 * c;
@@ -141,17 +148,24 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
 // ---- tiled kernel: a CTA takes a tile of query rows of ONE slot x one key/value head x one key split. Keys and values are
 // staged 32 at a time in shared memory with coalesced loads and shared by every (query row, query head of the group) pair of
 // the CTA, so a key/value row crosses the memory system once per CTA instead of once per pair. 8 warps, <= 4 pairs per warp.
+// A group of more than 32 query heads is cut into chunks of HC heads (blockIdx.y = group * chunks + chunk). When keys and
+// values are the same cached rows (kcache == vcache), the staged key tile is the value tile too. MAXC * 32 >= dv.
 constexpr int TL_KT = 32, TL_WARPS = 8, TL_PPW = 4;
 
-template <bool VEC>
-__global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a, int QT) {
+template <bool VEC, int MAXC>
+__global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a, int QT, int HC) {
     extern __shared__ float sm[];
-    const int HG = a.H / a.G, g = blockIdx.y, sp = blockIdx.z;
+    const int HGall = a.H / a.G, chunks = (HGall + HC - 1) / HC;
+    const int g = blockIdx.y / chunks, h0 = g * HGall + (blockIdx.y % chunks) * HC, HG = min(HC, g * HGall + HGall - h0);
+    const int sp = blockIdx.z;
     const int r0 = blockIdx.x * QT, nrows = min(QT, a.rows - r0), P = nrows * HG;
     const int dk = a.dk, dv = a.dv, dkp = VEC ? dk + 4 : (dk | 1);
-    float* sQ = sm;                              // [QT * HG][dk]
-    float* sK = sQ + (size_t)QT * HG * dk;       // [TL_KT][dkp]
-    float* sV = sK + TL_KT * dkp;                // [TL_KT][dv]
+    const bool shared_kv = a.vcache == a.kcache;
+    float* sQ = sm;                              // [QT * HC][dk]
+    float* sK = sQ + (size_t)QT * HC * dk;       // [TL_KT][dkp]
+    float* sV = sK + TL_KT * dkp;                // [TL_KT][dv] (unused when the key tile serves as the value tile)
+    const int vp = shared_kv ? dkp : dv;         // pitch of a staged value row
+    const float* sVal = shared_kv ? sK : sV;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int slot = a.row_slot[r0];
     int maxpos = -1;
@@ -159,7 +173,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
     if (maxpos < 0) return;
     for (int e = tid; e < P * dk; e += TL_WARPS * 32) {
         const int p = e / dk, d = e % dk;
-        sQ[e] = a.q[(size_t)(r0 + p / HG) * a.ldq + (size_t)(g * HG + p % HG) * dk + d];
+        sQ[e] = a.q[(size_t)(r0 + p / HG) * a.ldq + (size_t)(h0 + p % HG) * dk + d];
     }
     int lo = 0, hi = maxpos + 1;
     if (a.nsplit > 1) {
@@ -169,7 +183,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
     }
     const float* K = a.kcache + ((size_t)slot * a.G + g) * a.Smax * dk;
     const float* V = a.vcache + ((size_t)slot * a.G + g) * a.Smax * dv;
-    float m[TL_PPW], l[TL_PPW], o[TL_PPW][AT_MAXC];
+    float m[TL_PPW], l[TL_PPW], o[TL_PPW][MAXC];
     int ppos[TL_PPW];
 #pragma unroll
     for (int i = 0; i < TL_PPW; ++i) {
@@ -177,7 +191,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
         const int p = warp + TL_WARPS * i;
         ppos[i] = p < P ? a.row_pos[r0 + p / HG] : -1;
 #pragma unroll
-        for (int c = 0; c < AT_MAXC; ++c) o[i][c] = 0.f;
+        for (int c = 0; c < MAXC; ++c) o[i][c] = 0.f;
     }
     for (int j0 = lo; j0 < hi; j0 += TL_KT) {
         const int nk = min(TL_KT, hi - j0);
@@ -191,7 +205,8 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
         } else {
             for (int e = tid; e < nk * dk; e += TL_WARPS * 32) sK[(e / dk) * dkp + e % dk] = K[(size_t)j0 * dk + e];
         }
-        for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)j0 * dv + e];
+        if (!shared_kv)
+            for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)j0 * dv + e];
         __syncthreads();
         // The warp's pairs go through the tile TOGETHER: a lane reads its key row once for all of them, and a value element
         // once per key for all of them (shared-memory bandwidth, not the FMA pipe, limits this loop).
@@ -229,14 +244,14 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
             const int pos = ppos[i];
             if (pos < j0) continue;
             any = true;
-            const int head = g * HG + (warp + TL_WARPS * i) % HG;
+            const int head = h0 + (warp + TL_WARPS * i) % HG;
             const int j = j0 + lane;
             const bool valid = lane < nk && j <= pos;
             float sv = -INFINITY;
             if (valid) {
                 sv = sc[i] * a.scale;
                 if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
-                sv += a.rel[(size_t)a.bucket_of[pos - j] * a.H + head];
+                if (a.rel != nullptr) sv += a.rel[(size_t)a.bucket_of[pos - j] * a.H + head];
             }
             const float m_new = fmaxf(m[i], warp_max(sv));
             pr[i] = valid ? expf(sv - m_new) : 0.f;
@@ -244,16 +259,16 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
             l[i] = fmaf(l[i], corr, warp_sum(pr[i]));
             m[i] = m_new;
 #pragma unroll
-            for (int c = 0; c < AT_MAXC; ++c) o[i][c] *= corr;
+            for (int c = 0; c < MAXC; ++c) o[i][c] *= corr;
         }
         if (any) {
             for (int jj = 0; jj < nk; ++jj) {
                 float pj[TL_PPW];
 #pragma unroll
                 for (int i = 0; i < TL_PPW; ++i) pj[i] = __shfl_sync(0xffffffffu, pr[i], jj);
-                const float* vr = sV + jj * dv;
+                const float* vr = sVal + jj * vp;
 #pragma unroll
-                for (int c = 0; c < AT_MAXC; ++c) {
+                for (int c = 0; c < MAXC; ++c) {
                     const int d = lane + 32 * c;
                     if (d < dv) {
                         const float vv = vr[d];
@@ -268,19 +283,23 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
     for (int i = 0; i < TL_PPW; ++i) {
         const int p = warp + TL_WARPS * i;
         if (p >= P || ppos[i] < 0) continue;
-        const int row = r0 + p / HG, head = g * HG + p % HG;
+        const int row = r0 + p / HG, head = h0 + p % HG;
         if (a.nsplit > 1) {
             float* part = a.partial + ((size_t)(row * a.H + head) * a.nsplit + sp) * (dv + 2);
             if (lane == 0) { part[0] = m[i]; part[1] = l[i]; }
 #pragma unroll
-            for (int c = 0; c < AT_MAXC; ++c) {
+            for (int c = 0; c < MAXC; ++c) {
                 const int d = lane + 32 * c;
                 if (d < dv) part[2 + d] = o[i][c];
             }
         } else {
-            const float inv = 1.f / l[i];
+            float inv = 1.f / l[i];
+            if (a.sink != nullptr) {
+                const float sk = a.sink[head], mf = fmaxf(m[i], sk), c0 = expf(m[i] - mf);
+                inv = c0 / fmaf(l[i], c0, expf(sk - mf));
+            }
 #pragma unroll
-            for (int c = 0; c < AT_MAXC; ++c) {
+            for (int c = 0; c < MAXC; ++c) {
                 const int d = lane + 32 * c;
                 if (d < dv) a.out[(size_t)row * a.ldo + (size_t)head * dv + d] = o[i][c] * inv;
             }
@@ -289,6 +308,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
 }
 
 // one warp per (row, head): combines the key splits in split order; lane s first turns split s's (max, sum) into its weight
+template <int MAXC>
 __global__ void attn_merge_kernel(BiasAttnArgs a) {
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= a.rows * a.H) return;
@@ -298,7 +318,9 @@ __global__ void attn_merge_kernel(BiasAttnArgs a) {
     float mx = -INFINITY;
     for (int s = lane; s < a.nsplit; s += 32) mx = fmaxf(mx, part[(size_t)s * (a.dv + 2)]);
     mx = warp_max(mx);
-    float wgt[2] = {0.f, 0.f}, lsum = 0.f;   // nsplit <= 64: splits lane and lane + 32
+    const float sk = a.sink != nullptr ? a.sink[h] : -INFINITY;
+    mx = fmaxf(mx, sk);
+    float wgt[2] = {0.f, 0.f}, lsum = (a.sink != nullptr && lane == 0) ? expf(sk - mx) : 0.f;   // nsplit <= 64: splits lane and lane + 32
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int s = lane + 32 * i;
@@ -308,21 +330,21 @@ __global__ void attn_merge_kernel(BiasAttnArgs a) {
         }
     }
     const float inv = 1.f / warp_sum(lsum);
-    float acc[AT_MAXC];
+    float acc[MAXC];
 #pragma unroll
-    for (int c = 0; c < AT_MAXC; ++c) acc[c] = 0.f;
+    for (int c = 0; c < MAXC; ++c) acc[c] = 0.f;
     for (int s = 0; s < a.nsplit; ++s) {
         const float ws = __shfl_sync(0xffffffffu, s < 32 ? wgt[0] : wgt[1], s & 31);
         if (ws == 0.f) continue;
         const float* ps = part + (size_t)s * (a.dv + 2) + 2;
 #pragma unroll
-        for (int c = 0; c < AT_MAXC; ++c) {
+        for (int c = 0; c < MAXC; ++c) {
             const int d = lane + 32 * c;
             if (d < a.dv) acc[c] = fmaf(ps[d], ws, acc[c]);
         }
     }
 #pragma unroll
-    for (int c = 0; c < AT_MAXC; ++c) {
+    for (int c = 0; c < MAXC; ++c) {
         const int d = lane + 32 * c;
         if (d < a.dv) a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = acc[c] * inv;
     }
@@ -331,7 +353,8 @@ __global__ void attn_merge_kernel(BiasAttnArgs a) {
 int check_args(const BiasAttnArgs& a, const char* who) {
     B2_CHECK_ARG(a.q && a.kcache && a.vcache && a.row_slot && a.row_pos && a.rows > 0, "%s: null argument", who);
     B2_CHECK_ARG(a.H > 0 && a.G > 0 && a.H % a.G == 0, "%s: %d query heads cannot share %d key/value heads", who, a.H, a.G);
-    B2_CHECK_ARG(a.dk > 0 && a.dk <= 256 && a.dv > 0 && a.dv <= 32 * AT_MAXC, "%s: head sizes %d / %d exceed 256", who, a.dk, a.dv);
+    B2_CHECK_ARG(a.dk > 0 && a.dk <= 512 && a.dv > 0 && a.dv <= 512, "%s: head sizes %d / %d exceed 512", who, a.dk, a.dv);
+    B2_CHECK_ARG(a.vcache != a.kcache || a.dk == a.dv, "%s: keys that are also the values need dk == dv", who);
     return 0;
 }
 }  // namespace
@@ -345,42 +368,46 @@ int attn_prepare_f32(const BiasAttnArgs& a, cudaStream_t st) {
     return 0;
 }
 
+template <bool VEC, int MAXC>
+int launch_tile(const BiasAttnArgs& a, int QT, int HC, dim3 grid, size_t smem, cudaStream_t st) {
+    if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tile_kernel<VEC, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attn_tile_kernel<VEC, MAXC><<<grid, TL_WARPS * 32, smem, st>>>(a, QT, HC);
+    B2_LAUNCH_CHECK();
+    if (a.nsplit > 1) {
+        attn_merge_kernel<MAXC><<<(a.rows * a.H + 7) / 8, 256, 0, st>>>(a);
+        B2_LAUNCH_CHECK();
+    }
+    return 0;
+}
+
 int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t st) {
     B2_TRY(check_args(a, "attn_bias"));
-    B2_CHECK_ARG(a.out && a.rel && a.bucket_of, "attn_bias: null argument");
+    B2_CHECK_ARG(a.out && (a.rel == nullptr || a.bucket_of != nullptr), "attn_bias: null argument");
     B2_CHECK_ARG(a.nsplit >= 1 && a.nsplit <= 64 && (a.nsplit == 1 || a.partial != nullptr), "attn_bias: 1..64 key splits, with scratch");
     const int warps = a.rows * a.H;
     const bool vec = a.dk % 4 == 0 && (reinterpret_cast<uintptr_t>(a.kcache) & 15) == 0;
     const int HG = a.H / a.G;
-    if (HG <= TL_WARPS * TL_PPW && a.tile_rows >= 1) {
-        // query rows per CTA: as many as the 32 (row, head) pairs of a CTA allow; rows of a tile share their slot (tile_rows
-        // is 1 for a decode step, where every row has its own)
-        int QT = (TL_WARPS * TL_PPW) / HG;
+    if (a.tile_rows >= 1) {
+        // (row, head) pairs per CTA: 32. Query rows per CTA: as many as the heads of a chunk allow; rows of a tile share their
+        // slot (tile_rows is 1 for a decode step, where every row has its own)
+        const int HC = HG < TL_WARPS * TL_PPW ? HG : TL_WARPS * TL_PPW, chunks = (HG + HC - 1) / HC;
+        int QT = (TL_WARPS * TL_PPW) / HC;
         if (QT > a.tile_rows) QT = a.tile_rows;
         const int dkp = vec ? a.dk + 4 : (a.dk | 1);
-        const size_t smem = ((size_t)QT * HG * a.dk + (size_t)TL_KT * dkp + (size_t)TL_KT * a.dv) * sizeof(float);
-        dim3 grid((a.rows + QT - 1) / QT, a.G, a.nsplit);
-        if (vec) {
-            if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tile_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attn_tile_kernel<true><<<grid, TL_WARPS * 32, smem, st>>>(a, QT);
-        } else {
-            if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(attn_tile_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attn_tile_kernel<false><<<grid, TL_WARPS * 32, smem, st>>>(a, QT);
-        }
-        B2_LAUNCH_CHECK();
-        if (a.nsplit > 1) {
-            attn_merge_kernel<<<(warps + 7) / 8, 256, 0, st>>>(a);
-            B2_LAUNCH_CHECK();
-        }
-        return 0;
+        const bool shared_kv = a.vcache == a.kcache;
+        const size_t smem = ((size_t)QT * HC * a.dk + (size_t)TL_KT * dkp + (shared_kv ? 0 : (size_t)TL_KT * a.dv)) * sizeof(float);
+        dim3 grid((a.rows + QT - 1) / QT, a.G * chunks, a.nsplit);
+        if (a.dv <= 32 * AT_MAXC) return vec ? launch_tile<true, AT_MAXC>(a, QT, HC, grid, smem, st) : launch_tile<false, AT_MAXC>(a, QT, HC, grid, smem, st);
+        return vec ? launch_tile<true, 2 * AT_MAXC>(a, QT, HC, grid, smem, st) : launch_tile<false, 2 * AT_MAXC>(a, QT, HC, grid, smem, st);
     }
+    B2_CHECK_ARG(a.dk <= 256 && a.dv <= 32 * AT_MAXC, "attn_bias: the untiled kernel takes head sizes up to 256");
     dim3 grid((warps + AT_WARPS - 1) / AT_WARPS, a.nsplit);
     const size_t smem = (size_t)AT_WARPS * a.dk * sizeof(float);
     if (vec) attn_bias_kernel<true><<<grid, AT_WARPS * 32, smem, st>>>(a);
     else attn_bias_kernel<false><<<grid, AT_WARPS * 32, smem, st>>>(a);
     B2_LAUNCH_CHECK();
     if (a.nsplit > 1) {
-        attn_merge_kernel<<<(warps + 7) / 8, 256, 0, st>>>(a);
+        attn_merge_kernel<AT_MAXC><<<(warps + 7) / 8, 256, 0, st>>>(a);
         B2_LAUNCH_CHECK();
     }
     return 0;

@@ -286,6 +286,44 @@ int linear_f32(const LinearArgs& a, cudaStream_t stream);
 // out[r, :K] = bf16(A[r, :K]): the A operand of a tensor-core GEMM from fp32 activations (ld_out % 8 == 0)
 int cast_rows_bf16(const float* A, int64_t lda, void* out, int64_t ld_out, int M, int K, cudaStream_t stream);
 
+// Grouped Linear: output rows come in tiles of tile_rows (1 or 64) rows; tile t multiplies with the weight matrix of group
+// tile_group[t] (W + group * w_group_stride elements; a negative group: the tile is unused). Output row m reads input row
+// a_rows[m] (a_rows null: m / a_div; negative: a zero row). out[m, :N] = act(A[src] W_g^T); M bounds the rows (the launch grid).
+struct GroupedLinearArgs {
+    const float* A = nullptr; int64_t lda = 0;
+    const int32_t* a_rows = nullptr; int a_div = 1;
+    const void* W = nullptr; int64_t ldw = 0; int64_t w_group_stride = 0; int w_dtype = DT_F32;
+    const int32_t* tile_group = nullptr; int tile_rows = 64;
+    float* out = nullptr; int64_t ld_out = 0;
+    int M = 0, N = 0, K = 0;
+    int act = LIN_NONE;
+    int round_a = 0;
+};
+int linear_grouped_f32(const GroupedLinearArgs& g, cudaStream_t stream);
+enum { GROUPED_TILE_ROWS = 64 };
+
+// ---- mixture of experts (moe.cu) ------------------------------------------------------------------------------------------
+// Router: scores s = sigmoid(logits); experts form `groups` equal groups of neighbours, a group's score is the sum of its two
+// largest scores, only experts of the best `keep` groups compete; the `top` largest are chosen (ties: the lower index);
+// w = s / (sum of the chosen s + 1e-20) * scale. idx / w: [rows, top].
+struct MoeRouteArgs {
+    const float* logits = nullptr; int64_t ld = 0;
+    int rows = 0, experts = 0, top = 0, groups = 1, keep = 1;
+    float scale = 1.f;
+    int32_t* idx = nullptr; float* w = nullptr;
+};
+int moe_route_f32(const MoeRouteArgs& a, cudaStream_t stream);
+// Sorts the rows * top pairs by expert into tiles of `tile` rows of one expert each: pair_pos[pair] = its position,
+// src_row[position] = its token row (-1: padding), tile_group[t] = the expert of tile t (-1: unused).
+// max_tiles * tile >= rows * top + experts * (tile - 1).
+int moe_plan(const int32_t* idx, int rows, int top, int experts, int tile, int max_tiles, int32_t* pair_pos, int32_t* src_row, int32_t* tile_group,
+             cudaStream_t stream);
+// out[r, c] = silu(in[r, c]) * in[r, ff + c], c < ff
+int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t stream);
+// x[r] += alpha * sum_k w[r, k] * y[pair_pos[r * top + k]] (pair_pos null: the pair's own index)
+int moe_combine_f32(float* x, const float* y, int64_t ldy, const int32_t* pair_pos, const float* w, int rows, int top, int cols, float alpha,
+                    cudaStream_t stream);
+
 // ---- fp32 norms and row helpers (norms_f32.cu) ------------------------------------------------------------------------
 // x[r] += LayerNorm(y[r]) * gamma + beta   (normalisation of a sublayer's OUTPUT, added to the residual stream)
 int layernorm_add_f32(float* x, const float* y, const float* gamma, const float* beta, int rows, int cols, float eps, cudaStream_t stream);
@@ -297,6 +335,31 @@ int layernorm_gather_f32(const float* x, const int32_t* row_index, const float* 
 //   otherwise : out = unit_rms(y) * gamma * silu(z)            (RWKV mixer: per-head norm, then weight, then gate)
 int gated_group_rmsnorm_f32(const float* y, int64_t ldy, const float* z, int64_t ldz, const float* gamma, float* out, int64_t ldo, int rows,
                             int cols, int group, int gate_first, float eps, cudaStream_t stream);
+// ungated form; gamma_shared: one weight vector [group] for every group instead of [cols]
+int group_rmsnorm_f32(const float* y, int64_t ldy, const float* gamma, int gamma_shared, float* out, int64_t ldo, int rows, int cols, int group,
+                      float eps, cudaStream_t stream);
+// One-number RMS norm of pre-norm blocks: out[i] = x[row_index[i]] / sqrt(mean(x^2) + eps) * g[0] (row_index null: row i). With add
+// and/or vec the row is first updated in place, x += add[row] + vec: the opening of a pass of a looped block of layers.
+int rms_scalar_f32(float* x, const int32_t* row_index, const float* g, const float* add, const float* vec, float* out, int rows, int cols,
+                   float eps, cudaStream_t stream);
+// dst[b][c][r] = src[b][r][c], elements of 2 or 4 bytes (a stack of matrices transposed one by one)
+int transpose_blocks(const void* src, void* dst, int blocks, int rows, int cols, int elem_size, cudaStream_t stream);
+// PolyNorm: out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3, z = in + bias (bias nullable), N(u) = u / sqrt(mean(u^2) + eps) per row; coef on the device
+int polynorm_f32(const float* in, int64_t ld_in, const float* bias, const float* coef, float* out, int64_t ld_out, int rows, int cols, float eps,
+                 cudaStream_t stream);
+// x[i] = cap * tanh(x[i] / cap)
+int softcap_f32(float* x, size_t n, float cap, cudaStream_t stream);
+// out[r, h*dv + d] = a[r, h*dv + d] * sigmoid(g[r, h])
+int head_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, float* out, int64_t ldo, int rows, int heads, int dv, cudaStream_t stream);
+// x[row] = table[tok] + bigram[(prev * mul_prev + tok * mul_cur) mod buckets] (row `buckets` for a sequence's first token; bigram null:
+// no such term). Rows come as segments; the token in front of a call's first row is last_tok[slot], which is replaced by the segment's
+// last token. x0 (nullable) receives a copy of x. tokens is indexed by row.
+int embed_bigram_rows_f32(const int32_t* tokens, const SeqSeg* segs, int nseg, int max_n, const void* table, const void* bigram, int table_dtype,
+                          int32_t* last_tok, float* x, float* x0, int cols, int vocab, int buckets, int mul_prev, int mul_cur, int* err_flag,
+                          cudaStream_t stream);
+// cache[slot][pos][:rank] = unit_rms(in[r, :rank]) * gamma for every live row r
+int latent_append_f32(const float* in, int64_t ld_in, const float* gamma, float* cache, const int32_t* row_slot, const int32_t* row_pos, int rows,
+                      int rank, int Smax, float eps, cudaStream_t stream);
 // x[r, :] = table[tokens[r], :] as fp32; ids outside [0, vocab) give a zero row and raise *err_flag (B2_ERR_TOKEN_RANGE)
 int embed_rows_f32(const int32_t* tokens, const void* table, int table_dtype, float* x, int rows, int cols, int vocab, int* err_flag,
                    cudaStream_t stream);
@@ -318,11 +381,14 @@ int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out
 //   SCAN_SSD : dt = softplus(dt_raw + dt_bias[h]); S = exp(-exp(a_log[h]) dt) S + (dt k) v^T ; y = S^T q + skip[h] v
 //              (q, k: [rows, groups, dk] shared by heads/groups consecutive heads; v: [rows, heads, dv])
 //   SCAN_RWKV: y = (S + diag(bonus[h]) k v^T)^T q ; S = diag(exp(-exp(w_log))) S + k v^T    (q, k, w_log: [rows, heads, dk])
-enum { SCAN_SSD = 0, SCAN_RWKV = 1 };
+//   SCAN_HGRN2: f = l + (1 - l) sigmoid(z + b) per key channel; S = diag(f) S + (1 - f) v^T ; y = S^T silu(q)   (q, z: [rows, heads, dk]
+//              raw projections; l, b: [heads, dk]; there is no key input: what the gate forgets is what it writes)
+enum { SCAN_SSD = 0, SCAN_RWKV = 1, SCAN_HGRN2 = 2 };
 struct ScanArgs {
     int mode = SCAN_SSD;
     const float *q = nullptr, *k = nullptr, *v = nullptr; int64_t ldq = 0, ldk = 0, ldv = 0;
-    const float* decay_in = nullptr; int64_t ldd = 0;  // SSD: dt_raw [rows, heads]; RWKV: w_log [rows, heads*dk]
+    const float* decay_in = nullptr; int64_t ldd = 0;  // SSD: dt_raw [rows, heads]; RWKV: w_log [rows, heads*dk]; HGRN2: z [rows, heads*dk]
+    const float *gate_bias = nullptr, *gate_lower = nullptr;              // HGRN2, [heads, dk]
     const float *dt_bias = nullptr, *a_log = nullptr, *skip = nullptr;  // SSD, [heads]
     const float* bonus = nullptr;                                         // RWKV, [heads, dk]
     float* state = nullptr;                                               // [slots][heads][dk][dv]
@@ -337,14 +403,16 @@ struct BiasAttnArgs {
     float* q = nullptr; int64_t ldq = 0;          // [rows, H*dk]: normalised and scaled in place by attn_prepare
     const float* k = nullptr; int64_t ldk = 0;    // [rows, G*dk] projections of this call's rows
     const float* v = nullptr; int64_t ldv = 0;    // [rows, G*dv]
-    float* kcache = nullptr; float* vcache = nullptr;  // [slots][G][Smax][dk] / [..][dv] fp32
+    float* kcache = nullptr; float* vcache = nullptr;  // [slots][G][Smax][dk] / [..][dv] fp32; the same pointer (dk == dv): a cached row
+                                                       // is key and value at once
     float* out = nullptr; int64_t ldo = 0;        // [rows, H*dv]
-    const float* rel = nullptr;                   // [buckets, H] learned bias
+    const float* rel = nullptr;                   // [buckets, H] learned bias; null: no bias
     const int32_t* bucket_of = nullptr;           // [Smax]: bias row of a distance (built on the host)
     int H = 0, G = 0, dk = 0, dv = 0, Smax = 0, rows = 0;
     float eps = 0.f, scale = 1.f, softcap = 0.f;  // softcap <= 0: none
     float temp_coef = 0.f, temp_every = 1.f;      // q *= 1 + coef * ln(floor((p + 1) / every) + 1)
     const int32_t* row_slot = nullptr; const int32_t* row_pos = nullptr;
+    const float* sink = nullptr;                  // [H] or null: exp(sink[h]) joins the softmax denominator (no key, no value)
     float* partial = nullptr; int nsplit = 1;     // split-KV scratch [rows*H*nsplit*(dv+2)] when nsplit > 1
     int tile_rows = 0;                            // consecutive rows that share a slot (a prompt portion: its rows; a decode step: 1);
                                                   // 0: one warp per (row, head) without shared key/value tiles

@@ -242,7 +242,127 @@ int launch_linear(const LinearArgs& a, cudaStream_t st) {
     B2_LAUNCH_CHECK();
     return 0;
 }
+// ---- grouped Linear: every tile of output rows multiplies with the weight matrix of ITS group (mixture-of-experts) ------------
+// 64-row tiles: the tiled kernel above with a per-tile weight matrix and gathered input rows. Tiles without a group return.
+template <typename TW>
+__global__ void __launch_bounds__(256) linear_grouped_tiled_kernel(GroupedLinearArgs g) {
+    __shared__ float As[TK][TB + 4];
+    __shared__ float Ws[TK][TB + 4];
+    const int grp = g.tile_group[blockIdx.y];
+    if (grp < 0) return;
+    const TW* W = reinterpret_cast<const TW*>(g.W) + (size_t)grp * g.w_group_stride;
+    const int tid = threadIdx.x, M = g.M, N = g.N, K = g.K;
+    const int m0 = blockIdx.y * TB, n0 = blockIdx.x * TB;
+    const int tm = (tid >> 4) * 4, tn = (tid & 15) * 4;
+    // the tile's source rows: this thread stages rows r = (tid + e * 256) >> 4, e = 0..3
+    int src[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int m = m0 + ((tid + e * 256) >> 4);
+        src[e] = m < M ? (g.a_rows != nullptr ? g.a_rows[m] : m / g.a_div) : -1;
+    }
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int idx = tid + e * 256;
+            const int r = idx >> 4, kk = idx & 15;
+            const int k = k0 + kk;
+            float a = 0.f, w = 0.f;
+            if (k < K) {
+                if (src[e] >= 0) { a = g.A[(size_t)src[e] * g.lda + k]; if (g.round_a) a = round_bf16(a); }
+                if (n0 + r < N) w = ld_w(W + (size_t)(n0 + r) * g.ldw + k);
+            }
+            As[kk][r] = a;
+            Ws[kk][r] = w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < TK; ++kk) {
+            const float4 a = *reinterpret_cast<const float4*>(&As[kk][tm]);
+            const float4 w = *reinterpret_cast<const float4*>(&Ws[kk][tn]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, wv[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + tm + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tn + j;
+            if (n < N) lin_store(g.out + (size_t)m * g.ld_out + n, acc[i][j], nullptr, n, g.act, 1.f, 0);
+        }
+    }
+}
+
+// tiles of ONE row (a decode step: a handful of (token, choice) pairs): one warp per output column streams the weight row of
+// the pair's group; VEC reads 16 bytes of weights per lane and step
+template <typename TW, bool VEC>
+__global__ void __launch_bounds__(256) linear_grouped_rows_kernel(GroupedLinearArgs g) {
+    const int m = blockIdx.y;
+    const int grp = g.tile_group[m];
+    if (grp < 0) return;
+    const int src = g.a_rows != nullptr ? g.a_rows[m] : m / g.a_div;
+    if (src < 0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= g.N) return;
+    const TW* w = reinterpret_cast<const TW*>(g.W) + (size_t)grp * g.w_group_stride + (size_t)n * g.ldw;
+    const float* a = g.A + (size_t)src * g.lda;
+    float acc = 0.f;
+    if (VEC) {
+        for (int k0 = lane * 8; k0 < g.K; k0 += 256) {
+            float wv[8], av[8];
+            ld_w8(w + k0, wv);
+            ld_w8(a + k0, av);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = fmaf(g.round_a ? round_bf16(av[e]) : av[e], wv[e], acc);
+        }
+    } else {
+        for (int k = lane; k < g.K; k += 32) {
+            const float av = a[k];
+            acc = fmaf(g.round_a ? round_bf16(av) : av, ld_w(w + k), acc);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) lin_store(g.out + (size_t)m * g.ld_out + n, acc, nullptr, n, g.act, 1.f, 0);
+}
+
+template <typename TW>
+int launch_grouped(const GroupedLinearArgs& g, cudaStream_t st) {
+    if (g.tile_rows == 1) {
+        const bool vec = g.K % 8 == 0 && g.lda % 4 == 0 && g.ldw % 8 == 0 && g.w_group_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(g.W) & 15) == 0;
+        dim3 grid((g.N + 7) / 8, g.M);
+        if (vec) linear_grouped_rows_kernel<TW, true><<<grid, 256, 0, st>>>(g);
+        else linear_grouped_rows_kernel<TW, false><<<grid, 256, 0, st>>>(g);
+    } else {
+        dim3 grid((g.N + TB - 1) / TB, (g.M + TB - 1) / TB);
+        linear_grouped_tiled_kernel<TW><<<grid, 256, 0, st>>>(g);
+    }
+    B2_LAUNCH_CHECK();
+    return 0;
+}
 }  // namespace
+
+int linear_grouped_f32(const GroupedLinearArgs& g, cudaStream_t st) {
+    B2_CHECK_ARG(g.A && g.W && g.out && g.tile_group && g.M > 0 && g.N > 0 && g.K > 0, "linear_grouped: bad argument (M=%d N=%d K=%d)", g.M, g.N, g.K);
+    B2_CHECK_ARG(g.tile_rows == 1 || g.tile_rows == TB, "linear_grouped: tiles of 1 or %d rows", TB);
+    B2_CHECK_ARG(g.a_rows != nullptr || g.a_div >= 1, "linear_grouped: no source rows");
+    B2_CHECK_ARG(g.w_dtype == DT_F32 || g.w_dtype == DT_BF16, "linear_grouped: weights must be fp32 or bf16");
+    return g.w_dtype == DT_F32 ? launch_grouped<float>(g, st) : launch_grouped<__nv_bfloat16>(g, st);
+}
 
 namespace {
 __global__ void cast_rows_bf16_kernel(const float* __restrict__ A, int64_t lda, __nv_bfloat16* __restrict__ out, int64_t ld_out, int K) {

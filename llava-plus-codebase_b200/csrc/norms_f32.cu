@@ -1,6 +1,8 @@
 // fp32 normalisations and row helpers of the layer-list decoders: LayerNorm of a sublayer's output added to the residual
 // stream, gathered LayerNorm in front of the output head, grouped unit-RMS norm with a SiLU gate (before or after the
-// norm), embedding rows as fp32, the row map of a call. Statistics, sums and outputs are fp32 throughout; any width.
+// norm), embedding rows as fp32, the row map of a call; for pre-norm blocks: the one-number RMS norm (with the opening of a
+// looped pass folded in), PolyNorm, the logit soft-cap, per-head sigmoid gates, token + hashed-bigram embedding, and the
+// normalised latent row of a low-rank key/value cache. Statistics, sums and outputs are fp32 throughout; any width.
 #include "common.cuh"
 #include "kernels.h"
 
@@ -64,23 +66,24 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 // one warp per (row, group)
 __global__ void gated_group_rmsnorm_kernel(const float* __restrict__ y, int64_t ldy, const float* __restrict__ z, int64_t ldz,
                                            const float* __restrict__ gamma, float* __restrict__ out, int64_t ldo, int rows, int groups, int group,
-                                           int gate_first, float eps) {
+                                           int gate_first, int gamma_shared, float eps) {
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (w >= rows * groups) return;
     const int r = w / groups, g = w % groups;
     const float* yr = y + (size_t)r * ldy + (size_t)g * group;
-    const float* zr = z + (size_t)r * ldz + (size_t)g * group;
+    const float* zr = z != nullptr ? z + (size_t)r * ldz + (size_t)g * group : nullptr;   // null: no gate
+    const float* gm = gamma + (gamma_shared ? 0 : (size_t)g * group);                      // one weight vector for all groups, or one each
     float q = 0.f;
     for (int c = lane; c < group; c += 32) {
-        const float v = gate_first ? yr[c] * silu_f(zr[c]) : yr[c];
+        const float v = (gate_first && zr != nullptr) ? yr[c] * silu_f(zr[c]) : yr[c];
         q = fmaf(v, v, q);
     }
     q = warp_sum(q);
     const float rinv = 1.f / sqrtf(q / (float)group + eps);
     float* o = out + (size_t)r * ldo + (size_t)g * group;
     for (int c = lane; c < group; c += 32) {
-        const float gz = silu_f(zr[c]);
-        o[c] = gate_first ? (yr[c] * gz) * rinv * gamma[g * group + c] : yr[c] * rinv * gamma[g * group + c] * gz;
+        const float gz = zr != nullptr ? silu_f(zr[c]) : 1.f;
+        o[c] = gate_first ? (yr[c] * gz) * rinv * gm[c] : yr[c] * rinv * gm[c] * gz;
     }
 }
 
@@ -99,6 +102,121 @@ __global__ void sigmoid_gate_kernel(const float* __restrict__ a, int64_t lda, co
     const size_t r = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c < cols) out[r * ldo + c] = a[r * lda + c] / (1.f + expf(-g[r * ldg + c]));
+}
+
+// ---- pre-norm blocks with a one-number RMS norm -----------------------------------------------------------------------------
+// out[i] = x[row_index[i]] / sqrt(mean(x^2) + eps) * g[0]; with `add`/`vec` the row is first updated in place:
+// x += add[row] + vec (the opening of a pass of a looped block of layers)
+__global__ void rms_scalar_kernel(float* __restrict__ x, const int32_t* __restrict__ row_index, const float* __restrict__ g,
+                                  const float* __restrict__ add, const float* __restrict__ vec, float* __restrict__ out, int cols, float eps) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const size_t src = row_index != nullptr ? (size_t)row_index[r] : r;
+    float* xr = x + src * cols;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float v = xr[c];
+        if (add != nullptr || vec != nullptr) {
+            v += (add != nullptr ? add[src * cols + c] : 0.f) + (vec != nullptr ? vec[c] : 0.f);
+            xr[c] = v;
+        }
+        q = fmaf(v, v, q);
+    }
+    if (out == nullptr) return;   // only the update of x was asked for
+    const float mul = g[0] / sqrtf(block_sum(q, red) / (float)cols + eps);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) out[r * cols + c] = xr[c] * mul;
+}
+
+// dst[b][c][r] = src[b][r][c] for elements of 2 or 4 bytes
+template <typename T>
+__global__ void transpose_blocks_kernel(const T* __restrict__ src, T* __restrict__ dst, int rows, int cols) {
+    const size_t b = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < rows * cols) dst[b * rows * cols + (size_t)(i % cols) * rows + i / cols] = src[b * rows * cols + i];
+}
+
+// PolyNorm: out = a N(z) + b N(z^2) + c N(z^3) + e with z = in + bias, powers element-wise, N = division by the row's root mean square
+__global__ void polynorm_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ bias, const float* __restrict__ coef,
+                                float* __restrict__ out, int64_t ld_out, int cols, float eps) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const float* zr = in + r * ld_in;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float z = zr[c] + (bias != nullptr ? bias[c] : 0.f), z2 = z * z;
+        s2 += z2; s4 = fmaf(z2, z2, s4); s6 = fmaf(z2 * z2, z2, s6);
+    }
+    const float n = (float)cols;
+    const float r1 = coef[0] / sqrtf(block_sum(s2, red) / n + eps);
+    const float r2 = coef[1] / sqrtf(block_sum(s4, red) / n + eps);
+    const float r3 = coef[2] / sqrtf(block_sum(s6, red) / n + eps);
+    const float e = coef[3];
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        const float z = zr[c] + (bias != nullptr ? bias[c] : 0.f);
+        out[r * ld_out + c] = fmaf(z, fmaf(z, fmaf(z, r3, r2), r1), e);
+    }
+}
+
+// x[i] = cap * tanh(x[i] / cap)
+__global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+// out[r, h * dv + d] = a[r, h * dv + d] * sigmoid(g[r, h]): one gate per head
+__global__ void head_gate_kernel(const float* __restrict__ a, int64_t lda, const float* __restrict__ g, int64_t ldg, float* __restrict__ out,
+                                 int64_t ldo, int heads, int dv) {
+    const size_t r = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < heads * dv) out[r * ldo + c] = a[r * lda + c] / (1.f + expf(-g[r * ldg + c / dv]));
+}
+
+// Token embedding plus a hashed bigram row: x[row] = table[tok] + bigram[(prev * mul_prev + tok * mul_cur) mod buckets]; the first
+// token of a sequence takes row `buckets`. The previous token of a call's first row is the slot's carried token, which the same
+// block then replaces by the segment's last token. x0 (nullable) receives a copy of the rows.
+template <typename TT>
+__global__ void embed_bigram_kernel(const int32_t* __restrict__ tokens, const SeqSeg* __restrict__ segs, const TT* __restrict__ table,
+                                    const TT* __restrict__ bigram, int32_t* __restrict__ last_tok, float* __restrict__ x, float* __restrict__ x0,
+                                    int cols, int vocab, int buckets, int mul_prev, int mul_cur, int* err_flag) {
+    const SeqSeg sg = segs[blockIdx.y];
+    const int t = blockIdx.x;
+    if (t >= sg.n) return;
+    const size_t r = (size_t)sg.row0 + t;
+    const int tok = tokens[r];
+    int prev = -1;
+    if (t > 0) prev = tokens[r - 1];
+    else if (sg.pos0 > 0) prev = last_tok[sg.slot];
+    __syncthreads();   // every thread has read the carried token before thread 0 replaces it
+    if (t == 0 && threadIdx.x == 0) last_tok[sg.slot] = tokens[(size_t)sg.row0 + sg.n - 1];
+    const bool ok = tok >= 0 && tok < vocab && prev < vocab;
+    if (!ok && threadIdx.x == 0 && err_flag != nullptr) err_flag[0] = 1;  // slot 0 = B2_ERR_TOKEN_RANGE
+    long long brow = buckets;
+    if (prev >= 0) brow = (long long)(((unsigned long long)prev * (unsigned long long)mul_prev + (unsigned long long)tok * (unsigned long long)mul_cur) %
+                                      (unsigned long long)buckets);
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+        float v = 0.f;
+        if (ok) {
+            v = (float)table[(size_t)tok * cols + c];
+            if (bigram != nullptr) v += (float)bigram[(size_t)brow * cols + c];
+        }
+        x[r * cols + c] = v;
+        if (x0 != nullptr) x0[r * cols + c] = v;
+    }
+}
+
+// latent[slot][pos] = unit_rms(in[r]) * gamma: the normalised low-rank row that a token leaves in the cache
+__global__ void latent_append_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ gamma, float* __restrict__ cache,
+                                     const int32_t* __restrict__ row_slot, const int32_t* __restrict__ row_pos, int rank, int Smax, float eps) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const int pos = row_pos[r];
+    if (pos < 0) return;
+    const float* src = in + r * ld_in;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) q = fmaf(src[c], src[c], q);
+    const float mul = 1.f / sqrtf(block_sum(q, red) / (float)rank + eps);
+    float* dst = cache + ((size_t)row_slot[r] * Smax + pos) * rank;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = src[c] * mul * gamma[c];
 }
 
 __global__ void rowmap_portion_kernel(SeqSeg* segs, int32_t* row_slot, int32_t* row_pos, int32_t* len, int slot, int n, int restart) {
@@ -145,7 +263,16 @@ int gated_group_rmsnorm_f32(const float* y, int64_t ldy, const float* z, int64_t
     B2_CHECK_ARG(y && z && gamma && out && rows > 0 && group > 0 && cols % group == 0, "gated_group_rmsnorm: cols %d is not a multiple of the group %d",
                  cols, group);
     const int groups = cols / group, warps = rows * groups;
-    gated_group_rmsnorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(y, ldy, z, ldz, gamma, out, ldo, rows, groups, group, gate_first, eps);
+    gated_group_rmsnorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(y, ldy, z, ldz, gamma, out, ldo, rows, groups, group, gate_first, 0, eps);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int group_rmsnorm_f32(const float* y, int64_t ldy, const float* gamma, int gamma_shared, float* out, int64_t ldo, int rows, int cols, int group,
+                      float eps, cudaStream_t st) {
+    B2_CHECK_ARG(y && gamma && out && rows > 0 && group > 0 && cols % group == 0, "group_rmsnorm: cols %d is not a multiple of the group %d", cols, group);
+    const int groups = cols / group, warps = rows * groups;
+    gated_group_rmsnorm_kernel<<<(warps + 7) / 8, 256, 0, st>>>(y, ldy, nullptr, 0, gamma, out, ldo, rows, groups, group, 0, gamma_shared, eps);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -164,6 +291,71 @@ int embed_rows_f32(const int32_t* tokens, const void* table, int table_dtype, fl
 int sigmoid_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, float* out, int64_t ldo, int rows, int cols, cudaStream_t st) {
     B2_CHECK_ARG(a && g && out && rows > 0 && cols > 0, "sigmoid_gate: bad argument");
     sigmoid_gate_kernel<<<dim3((cols + 255) / 256, rows), 256, 0, st>>>(a, lda, g, ldg, out, ldo, cols);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int rms_scalar_f32(float* x, const int32_t* row_index, const float* g, const float* add, const float* vec, float* out, int rows, int cols,
+                   float eps, cudaStream_t st) {
+    B2_CHECK_ARG(x && rows > 0 && cols > 0 && ((g && out) || (!out && (add || vec))), "rms_scalar: bad argument");
+    rms_scalar_kernel<<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(x, row_index, g, add, vec, out, cols, eps);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int transpose_blocks(const void* src, void* dst, int blocks, int rows, int cols, int elem_size, cudaStream_t st) {
+    B2_CHECK_ARG(src && dst && blocks > 0 && rows > 0 && cols > 0 && (elem_size == 2 || elem_size == 4), "transpose_blocks: bad argument");
+    dim3 grid((rows * cols + 255) / 256, blocks);
+    if (elem_size == 2) transpose_blocks_kernel<uint16_t><<<grid, 256, 0, st>>>(reinterpret_cast<const uint16_t*>(src), reinterpret_cast<uint16_t*>(dst), rows, cols);
+    else transpose_blocks_kernel<uint32_t><<<grid, 256, 0, st>>>(reinterpret_cast<const uint32_t*>(src), reinterpret_cast<uint32_t*>(dst), rows, cols);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int polynorm_f32(const float* in, int64_t ld_in, const float* bias, const float* coef, float* out, int64_t ld_out, int rows, int cols, float eps,
+                 cudaStream_t st) {
+    B2_CHECK_ARG(in && coef && out && rows > 0 && cols > 0, "polynorm: bad argument");
+    polynorm_kernel<<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(in, ld_in, bias, coef, out, ld_out, cols, eps);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int softcap_f32(float* x, size_t n, float cap, cudaStream_t st) {
+    B2_CHECK_ARG(x && n > 0 && cap > 0.f, "softcap: bad argument");
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, cap);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int head_gate_f32(const float* a, int64_t lda, const float* g, int64_t ldg, float* out, int64_t ldo, int rows, int heads, int dv, cudaStream_t st) {
+    B2_CHECK_ARG(a && g && out && rows > 0 && heads > 0 && dv > 0, "head_gate: bad argument");
+    head_gate_kernel<<<dim3((heads * dv + 255) / 256, rows), 256, 0, st>>>(a, lda, g, ldg, out, ldo, heads, dv);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int embed_bigram_rows_f32(const int32_t* tokens, const SeqSeg* segs, int nseg, int max_n, const void* table, const void* bigram, int table_dtype,
+                          int32_t* last_tok, float* x, float* x0, int cols, int vocab, int buckets, int mul_prev, int mul_cur, int* err_flag,
+                          cudaStream_t st) {
+    B2_CHECK_ARG(tokens && segs && table && last_tok && x && nseg > 0 && max_n > 0, "embed_bigram_rows: bad argument");
+    B2_CHECK_ARG(bigram == nullptr || buckets > 0, "embed_bigram_rows: a bigram table needs buckets");
+    if (bigram == nullptr) buckets = 1;
+    if (table_dtype == DT_F32)
+        embed_bigram_kernel<float><<<dim3(max_n, nseg), 128, 0, st>>>(tokens, segs, reinterpret_cast<const float*>(table),
+                                                                     reinterpret_cast<const float*>(bigram), last_tok, x, x0, cols, vocab, buckets,
+                                                                     mul_prev, mul_cur, err_flag);
+    else
+        embed_bigram_kernel<__nv_bfloat16><<<dim3(max_n, nseg), 128, 0, st>>>(tokens, segs, reinterpret_cast<const __nv_bfloat16*>(table),
+                                                                             reinterpret_cast<const __nv_bfloat16*>(bigram), last_tok, x, x0, cols,
+                                                                             vocab, buckets, mul_prev, mul_cur, err_flag);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int latent_append_f32(const float* in, int64_t ld_in, const float* gamma, float* cache, const int32_t* row_slot, const int32_t* row_pos, int rows,
+                      int rank, int Smax, float eps, cudaStream_t st) {
+    B2_CHECK_ARG(in && gamma && cache && row_slot && row_pos && rows > 0 && rank > 0, "latent_append: bad argument");
+    latent_append_kernel<<<rows, rank >= 512 ? 256 : 128, 0, st>>>(in, ld_in, gamma, cache, row_slot, row_pos, rank, Smax, eps);
     B2_LAUNCH_CHECK();
     return 0;
 }

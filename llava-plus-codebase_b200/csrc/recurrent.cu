@@ -1,5 +1,5 @@
 // Recurrent mixers of the layer-list decoders: causal depthwise convolution with a carried tail, RWKV token shift, and the
-// linear recurrence with a diagonal decay over a per-head [key, value] state (state-space and RWKV forms). One code path
+// linear recurrence with a diagonal decay over a per-head [key, value] state (state-space, RWKV and HGRN2 forms). One code path
 // serves a portion of a prompt (n rows of one slot) and a decode step (one row of each of B slots): the rows come as
 // segments (kernels.h, SeqSeg). State, decays, step sizes and sums are fp32; a segment whose pos0 is 0 starts from zero
 // state whatever its slot held before, so a slot that is handed to a new request needs no clearing.
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
     float* sD = sK + TT * dkp;         // [TT][dkp] decay per key channel
     float* sV = sD + TT * dkp;         // [TT][32]
     float* sR = sV + TT * 32;          // [TT][KS][32] partial outputs of a tile
-    const int g = MODE == SCAN_SSD ? h / (a.heads / a.groups) : h;
+    const int g = MODE == SCAN_SSD ? h / (a.heads / a.groups) : h;  // SCAN_HGRN2 has no key input: a.k is not read
     const bool col_ok = j < dv;
     float S[KPT], bon[KPT];
     float* st = a.state + (((size_t)sg.slot * a.heads + h) * dk) * dv;
@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
             if (t < nt && key < dk) {
                 const size_t row = (size_t)(sg.row0 + t0 + t);
                 rq[u] = a.q[row * a.ldq + (size_t)g * dk + key];
-                rk[u] = a.k[row * a.ldk + (size_t)g * dk + key];
-                if (MODE == SCAN_RWKV) rd[u] = a.decay_in[row * a.ldd + (size_t)h * dk + key];
+                if (MODE != SCAN_HGRN2) rk[u] = a.k[row * a.ldk + (size_t)g * dk + key];
+                if (MODE != SCAN_SSD) rd[u] = a.decay_in[row * a.ldd + (size_t)h * dk + key];
             }
         }
 #pragma unroll
@@ -185,8 +185,18 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
 #pragma unroll
         for (int u = 0; u < EPT; ++u) {
             const int e = tid + u * nthr, key = e % dkp;
-            sQ[e] = rq[u]; sK[e] = rk[u];
-            if (MODE == SCAN_RWKV) sD[e] = key < dk ? expf(-expf(rd[u])) : 1.f;
+            if (MODE == SCAN_HGRN2) {
+                // forget gate bounded below: f = l + (1 - l) sigmoid(z + b); what is forgotten, 1 - f, is what is written
+                float f = 1.f;
+                if (key < dk) {
+                    const float low = a.gate_lower[(size_t)h * dk + key];
+                    f = fmaf(1.f - low, 1.f / (1.f + expf(-(rd[u] + a.gate_bias[(size_t)h * dk + key]))), low);
+                }
+                sQ[e] = silu_f(rq[u]); sK[e] = 1.f - f; sD[e] = f;
+            } else {
+                sQ[e] = rq[u]; sK[e] = rk[u];
+                if (MODE == SCAN_RWKV) sD[e] = key < dk ? expf(-expf(rd[u])) : 1.f;
+            }
         }
         // SSD: the decay and the step size are scalars per token; the step size multiplies the value (dt B x^T = B (dt x)^T),
         // so the keys are staged as they are and sD holds [TT] step sizes followed by [TT] decays
@@ -215,7 +225,7 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
                     const float4 k4 = *reinterpret_cast<const float4*>(sK + t * dkp + ks * KPT + i4 * 4);
                     q[i4 * 4] = q4.x; q[i4 * 4 + 1] = q4.y; q[i4 * 4 + 2] = q4.z; q[i4 * 4 + 3] = q4.w;
                     k[i4 * 4] = k4.x; k[i4 * 4 + 1] = k4.y; k[i4 * 4 + 2] = k4.z; k[i4 * 4 + 3] = k4.w;
-                    if (MODE == SCAN_RWKV) {
+                    if (MODE != SCAN_SSD) {
                         const float4 d4 = *reinterpret_cast<const float4*>(sD + t * dkp + ks * KPT + i4 * 4);
                         d[i4 * 4] = d4.x; d[i4 * 4 + 1] = d4.y; d[i4 * 4 + 2] = d4.z; d[i4 * 4 + 3] = d4.w;
                     }
@@ -228,6 +238,9 @@ __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
                     if (MODE == SCAN_RWKV) {
                         acc = fmaf(q[i], fmaf(bon[i], kv, S[i]), acc);
                         S[i] = fmaf(d[i], S[i], kv);
+                    } else if (MODE == SCAN_HGRN2) {
+                        S[i] = fmaf(d[i], S[i], kv);
+                        acc = fmaf(q[i], S[i], acc);
                     } else {
                         S[i] = fmaf(dec, S[i], kv);
                         acc = fmaf(q[i], S[i], acc);
@@ -295,7 +308,7 @@ int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out
 }
 
 int linear_scan_f32(const ScanArgs& a, cudaStream_t st) {
-    B2_CHECK_ARG(a.q && a.k && a.v && a.decay_in && a.state && a.y && a.segs && a.nseg > 0, "linear_scan: null argument");
+    B2_CHECK_ARG(a.q && (a.k || a.mode == SCAN_HGRN2) && a.v && a.decay_in && a.state && a.y && a.segs && a.nseg > 0, "linear_scan: null argument");
     B2_CHECK_ARG(a.heads > 0 && a.dk > 0 && a.dv > 0, "linear_scan: bad sizes");
     const int KS = (a.dk + KPT - 1) / KPT;
     B2_CHECK_ARG(KS <= 16, "linear_scan: key size %d exceeds %d", a.dk, 16 * KPT);
@@ -305,6 +318,10 @@ int linear_scan_f32(const ScanArgs& a, cudaStream_t st) {
         B2_CHECK_ARG(a.groups > 0 && a.heads % a.groups == 0 && a.dt_bias && a.a_log && a.skip, "linear_scan(ssd): heads %d / groups %d", a.heads, a.groups);
         if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_SSD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         linear_scan_kernel<SCAN_SSD><<<grid, block, smem, st>>>(a);
+    } else if (a.mode == SCAN_HGRN2) {
+        B2_CHECK_ARG(a.gate_bias && a.gate_lower, "linear_scan(hgrn2): null gate bias / lower bound");
+        if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_HGRN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        linear_scan_kernel<SCAN_HGRN2><<<grid, block, smem, st>>>(a);
     } else {
         B2_CHECK_ARG(a.bonus != nullptr, "linear_scan(rwkv): null bonus");
         if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_RWKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

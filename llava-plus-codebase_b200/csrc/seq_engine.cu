@@ -20,6 +20,11 @@ struct SeqWeights {   // tensors of one layer that owns its weights
     DevBuf lproj_w, rel, lo_w;                                                           // attention: [q | k | v | g] fused
     DevBuf mu, r_w, k_w, v_w, g_w, w1, w2, w0, bonus, rnorm, ro_w;                       // RWKV
     DevBuf up_w, down_w;                                                                 // feed-forward
+    // pre-norm designs
+    DevBuf qdg_w, dkv_norm, ukT, uv_w, sink;            // latent attention: [q | dkv | g] fused; W_uk per head transposed to [rank][dim]
+    DevBuf qfv_w, f_b, lower, hnorm;                    // HGRN2: [q | f | v] fused
+    DevBuf up_b, down_b, down_b16, act_coef;            // PolyNorm feed-forward (bias of the second product also as bf16: GEMM epilogue)
+    DevBuf router_w, egu_w, ed_w, sgu_w, sd_w;          // experts: [E][gate | up][width], [E][width][ff]; shared expert [gate | up], down
     std::map<std::string, int> got;
 };
 
@@ -31,13 +36,23 @@ struct SeqLayerInfo {
     int nq = 0, nk = 0, nv = 0, ng = 0, lproj = 0;    // attention projection widths
     int rn = 0;                                       // RWKV heads*dim
     int dproj_ld = 0, lproj_ld = 0;                   // row pitch of the projection outputs (multiples of 8: tensor-core epilogue)
+    int pq = 0, pproj = 0, pproj_ld = 0;              // latent attention / HGRN2: width of q, of the fused projection, its pitch
+    int pv = 0;                                       // heads * vdim of those mixers
 };
+struct SeqRun { int layer; int pass; };               // one layer run; pass >= 0: the run opens pass `pass` of the looped block
 
 struct SeqModel {
     b2_seq_model_desc d;
     std::vector<SeqLayerInfo> layers;
+    std::vector<SeqRun> runs;          // what one forward pass executes, in order (a looped layer appears once per pass)
     std::vector<SeqWeights> w;
     DevBuf embed, head, final_w, final_b;
+    DevBuf bigram, loop_step;          // [buckets + 1, width] in the weight dtype; [times, width] fp32
+    DevBuf x0;                         // the embedding output, kept for the passes of a looped block
+    DevBuf qabs, olat;                 // latent attention: queries carried into the latent space, latent-space outputs [rows, heads*rank]
+    DevBuf ffa;                        // activated feed-forward rows
+    DevBuf rlogit, moe_idx, moe_w, moe_pos, moe_src, moe_tile, moe_h, moe_a, moe_y;   // router and grouped expert products
+    int lat_w = 0, moe_rows = 0, moe_tiles = 0, moe_hw = 0, moe_aw = 0, moe_top = 0, moe_e = 0;
     std::map<std::string, int> got;
     int w_dtype = DT_BF16;             // dtype of the Linear weights and the embedding table on the device
     int rows = 0;                      // workspace rows
@@ -53,9 +68,12 @@ struct SeqLayerState {
     DevBuf ssm, conv_tail;             // mamba2: [slots][heads][state][vdim], [slots][taps-1][channels]
     DevBuf kc, vc, bucket_of;          // attention: [slots][G][Smax][dk], [slots][G][Smax][dv], int32 [Smax]
     DevBuf wkv, prev;                  // RWKV: [slots][heads][dim][dim], [slots][width]
+    DevBuf lat;                        // latent attention: [slots][Smax][rank]
+    DevBuf gla;                        // HGRN2: [slots][heads][dim][vdim]
 };
 struct SeqState {
-    std::vector<SeqLayerState> layer;
+    std::vector<SeqLayerState> layer;  // one per layer RUN
+    DevBuf last_tok;                   // int32 [slots]: the token in front of the next one (hashed bigram embedding)
     DevBuf attn_partial;
     int nsplit_max = 1;
 };
@@ -129,7 +147,7 @@ struct Lin {  // one Linear call on the model's compute dtype
     const b2_model* m;
     cudaStream_t st;
     int operator()(const float* A, int64_t lda, const DevBuf& W, int N, int K, float* out, int64_t ldo, int M, int act = LIN_NONE,
-                   float alpha = 1.f, int accumulate = 0, const float* bias = nullptr, size_t w_row0 = 0) const {
+                   float alpha = 1.f, int accumulate = 0, const float* bias = nullptr, size_t w_row0 = 0, const void* bias16 = nullptr) const {
         LinearArgs a;
         const SeqModel& s = *m->seq;
         a.A = A; a.lda = lda; a.ldw = K; a.w_dtype = s.w_dtype;
@@ -139,11 +157,14 @@ struct Lin {  // one Linear call on the model's compute dtype
         // bf16 compute, a portion of a prompt: the tcgen05 GEMM on a bf16 copy of A (weights are stored with their rows
         // padded to a multiple of 8, zero-filled, so N rounds up; the pitch of every projection buffer is a multiple of 8)
         const int Np = (N + 7) / 8 * 8;
-        if (a.round_a && M >= tc_min_rows() && N >= 32 && K % 8 == 0 && K >= 32 && K <= s.a16_w && ldo % 8 == 0 && Np <= ldo && bias == nullptr &&
-            w_row0 == 0 && tc_enabled()) {
+        // a block of rows inside a matrix (w_row0 > 0) has no zero rows behind it: then N itself must be a multiple of 8; a bias
+        // rides the epilogue as bf16
+        if (a.round_a && M >= tc_min_rows() && N >= 32 && K % 8 == 0 && K >= 32 && K <= s.a16_w && ldo % 8 == 0 && Np <= ldo &&
+            (bias == nullptr || bias16 != nullptr) && (w_row0 == 0 || (N % 8 == 0 && (w_row0 * (size_t)K) % 8 == 0)) &&
+            (reinterpret_cast<uintptr_t>(out) & 15) == 0 && tc_enabled()) {
             B2_TRY(cast_rows_bf16(A, lda, s.a16.p, K, M, K, st));
             GemmArgs g;
-            g.A = s.a16.p; g.lda = K; g.W = W.p; g.ldw = K; g.out = out; g.ld_out = (int)ldo; g.out_fp32 = 1;
+            g.A = s.a16.p; g.lda = K; g.W = a.W; g.ldw = K; g.out = out; g.ld_out = (int)ldo; g.out_fp32 = 1; g.bias = bias16;
             g.M = M; g.N = Np; g.K = K; g.act = ACT_NONE; g.post = act; g.alpha = alpha; g.accumulate = accumulate;
             return gemm_bf16(g, st);
         }
@@ -177,11 +198,125 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
     float* mix = s.mixout.as<float>();
     const SeqSeg* segs = s.segs.as<SeqSeg>();
     const int max_n = nseg == 1 ? R : 1;  // a prompt portion is one segment of R rows; a decode step is R segments of one row
-    for (size_t li = 0; li < s.layers.size(); ++li) {
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1;
+    const float rm = s.d.residual_mult;
+    float* xn = s.xn.as<float>();
+    for (size_t ri = 0; ri < s.runs.size(); ++ri) {
+        const size_t li = (size_t)s.runs[ri].layer;
         const SeqLayerInfo& L = s.layers[li];
         const b2_seq_layer_desc& d = L.d;
         SeqWeights& W = s.w[L.src];
-        SeqLayerState& S = state.layer[li];
+        SeqLayerState& S = state.layer[ri];
+        // a run that opens a pass of the looped block: x += (the embedding output, from the second pass on) + the pass's vector
+        const int pass = s.runs[ri].pass;
+        const float* pass_add = pass > 0 ? s.x0.as<float>() : nullptr;
+        const float* pass_vec = pass >= 0 ? s.loop_step.as<float>() + (size_t)pass * width : nullptr;
+        if (pre) {
+            // pre-norm block: the mixer reads xn = g1 * unit_rms(x) and adds residual_mult * its output onto x in its last product
+            B2_TRY(rms_scalar_f32(x, nullptr, W.norm1.as<float>(), pass_add, pass_vec, xn, R, width, eps, st));
+            if (d.type == B2_MIXER_LATENT_ATTN) {
+                float* proj = s.proj.as<float>();  // [R, q | dkv | g]
+                const int H = d.la_heads, dk = d.la_dim, dv = d.la_vdim, rank = d.la_rank;
+                B2_TRY(lin(xn, width, W.qdg_w, L.pproj, width, proj, L.pproj_ld, R));
+                B2_TRY(latent_append_f32(proj + L.pq, L.pproj_ld, W.dkv_norm.as<float>(), S.lat.as<float>(), s.row_slot.as<int32_t>(),
+                                         s.row_pos.as<int32_t>(), R, rank, kv->max_seq, eps, st));
+                // absorbed form: q_h -> W_uk_h^T q_h lives in the latent space, so scores and values read the cached rows directly
+                float* qabs = s.qabs.as<float>();
+                const int64_t lq = (int64_t)H * rank;
+                for (int h = 0; h < H; ++h)
+                    B2_TRY(lin(proj + (size_t)h * dk, L.pproj_ld, W.ukT, rank, dk, qabs + (size_t)h * rank, lq, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * rank));
+                BiasAttnArgs aa;
+                aa.q = qabs; aa.ldq = lq;
+                aa.kcache = S.lat.as<float>(); aa.vcache = S.lat.as<float>();
+                aa.out = s.olat.as<float>(); aa.ldo = lq;
+                aa.sink = W.sink.as<float>();
+                aa.H = H; aa.G = 1; aa.dk = rank; aa.dv = rank; aa.Smax = kv->max_seq; aa.rows = R;
+                aa.eps = eps; aa.scale = d.la_scale; aa.softcap = 0.f;
+                aa.row_slot = s.row_slot.as<int32_t>(); aa.row_pos = s.row_pos.as<int32_t>();
+                aa.nsplit = attn_nsplit(R, (H + 31) / 32, kv->max_seq);
+                aa.tile_rows = max_n;
+                if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
+                aa.partial = state.attn_partial.as<float>();
+                B2_TRY(attn_bias_f32(aa, st));
+                float* y = s.y.as<float>();
+                for (int h = 0; h < H; ++h)
+                    B2_TRY(lin(s.olat.as<float>() + (size_t)h * rank, lq, W.uv_w, dv, rank, y + (size_t)h * dv, L.pv, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * dv));
+                B2_TRY(head_gate_f32(y, L.pv, proj + L.pq + rank, L.pproj_ld, s.gated.as<float>(), L.pv, R, H, dv, st));
+                B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, x, width, R, LIN_NONE, rm, 1));
+            } else {
+                float* proj = s.proj.as<float>();  // [R, q | f | v]
+                const int H = d.g_heads, dk = d.g_dim, dv = d.g_vdim;
+                B2_TRY(lin(xn, width, W.qfv_w, L.pproj, width, proj, L.pproj_ld, R));
+                ScanArgs sa;
+                sa.mode = SCAN_HGRN2;
+                sa.q = proj; sa.ldq = L.pproj_ld;
+                sa.decay_in = proj + L.pq; sa.ldd = L.pproj_ld;
+                sa.v = proj + 2 * L.pq; sa.ldv = L.pproj_ld;
+                sa.gate_bias = W.f_b.as<float>(); sa.gate_lower = W.lower.as<float>();
+                sa.state = S.gla.as<float>();
+                sa.y = s.y.as<float>(); sa.ldy = L.pv;
+                sa.heads = H; sa.groups = H; sa.dk = dk; sa.dv = dv;
+                sa.segs = segs; sa.nseg = nseg;
+                B2_TRY(linear_scan_f32(sa, st));
+                B2_TRY(group_rmsnorm_f32(s.y.as<float>(), L.pv, W.hnorm.as<float>(), 1, s.gated.as<float>(), L.pv, R, L.pv, dv, eps, st));
+                B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, x, width, R, LIN_NONE, rm, 1));
+            }
+            if (d.ff > 0) {
+                B2_TRY(rms_scalar_f32(x, nullptr, W.norm2.as<float>(), nullptr, nullptr, xn, R, width, eps, st));
+                if (d.ff_kind == B2_FF_POLYNORM) {
+                    const int ffl = (d.ff + 7) / 8 * 8;
+                    B2_TRY(lin(xn, width, W.up_w, d.ff, width, s.ff.as<float>(), ffl, R));
+                    B2_TRY(polynorm_f32(s.ff.as<float>(), ffl, W.up_b.as<float>(), W.act_coef.as<float>(), s.ffa.as<float>(), d.ff, R, d.ff, eps, st));
+                    B2_TRY(lin(s.ffa.as<float>(), d.ff, W.down_w, width, d.ff, x, width, R, LIN_NONE, rm, 1, W.down_b.as<float>(), 0, W.down_b16.p));
+                } else if (d.ff_kind == B2_FF_MOE) {
+                    const int E = d.moe_experts, top = d.moe_top, ff = d.ff;
+                    B2_TRY(lin(xn, width, W.router_w, E, width, s.rlogit.as<float>(), (E + 7) / 8 * 8, R));
+                    MoeRouteArgs ra;
+                    ra.logits = s.rlogit.as<float>(); ra.ld = (E + 7) / 8 * 8; ra.rows = R; ra.experts = E; ra.top = top;
+                    ra.groups = d.moe_groups; ra.keep = d.moe_keep; ra.scale = d.moe_scale;
+                    ra.idx = s.moe_idx.as<int32_t>(); ra.w = s.moe_w.as<float>();
+                    B2_TRY(moe_route_f32(ra, st));
+                    if (d.moe_shared_ff > 0) {
+                        const int sf = d.moe_shared_ff, sfl = (2 * sf + 7) / 8 * 8;
+                        B2_TRY(lin(xn, width, W.sgu_w, 2 * sf, width, s.ff.as<float>(), sfl, R));
+                        B2_TRY(swiglu_rows_f32(s.ff.as<float>(), sfl, s.ffa.as<float>(), sf, R, sf, st));
+                        B2_TRY(lin(s.ffa.as<float>(), sf, W.sd_w, width, sf, x, width, R, LIN_NONE, rm, 1));
+                    }
+                    // routed experts: (token, choice) pairs as rows of grouped products. A decode step keeps the pairs where
+                    // they are (tiles of one row); a prompt portion sorts them by expert into tiles of 64 rows.
+                    GroupedLinearArgs ga;
+                    ga.A = xn; ga.lda = width; ga.W = W.egu_w.p; ga.ldw = width; ga.w_group_stride = (int64_t)2 * ff * width; ga.w_dtype = s.w_dtype;
+                    ga.out = s.moe_h.as<float>(); ga.ld_out = 2 * ff; ga.N = 2 * ff; ga.K = width; ga.round_a = s.d.compute == B2_COMPUTE_BF16;
+                    const int32_t* pos = nullptr;
+                    int P = R * top;
+                    if (R <= 8) {
+                        ga.tile_rows = 1; ga.tile_group = s.moe_idx.as<int32_t>(); ga.a_div = top; ga.M = P;
+                    } else {
+                        const int tiles = (R * top + E * (GROUPED_TILE_ROWS - 1) + GROUPED_TILE_ROWS - 1) / GROUPED_TILE_ROWS;
+                        B2_TRY(moe_plan(s.moe_idx.as<int32_t>(), R, top, E, GROUPED_TILE_ROWS, tiles, s.moe_pos.as<int32_t>(), s.moe_src.as<int32_t>(),
+                                        s.moe_tile.as<int32_t>(), st));
+                        pos = s.moe_pos.as<int32_t>();
+                        P = tiles * GROUPED_TILE_ROWS;
+                        ga.tile_rows = GROUPED_TILE_ROWS; ga.tile_group = s.moe_tile.as<int32_t>(); ga.a_rows = s.moe_src.as<int32_t>(); ga.M = P;
+                    }
+                    B2_TRY(linear_grouped_f32(ga, st));
+                    B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, s.moe_a.as<float>(), ff, P, ff, st));
+                    GroupedLinearArgs gd = ga;
+                    gd.A = s.moe_a.as<float>(); gd.lda = ff; gd.a_rows = nullptr; gd.a_div = 1;
+                    gd.W = W.ed_w.p; gd.ldw = ff; gd.w_group_stride = (int64_t)width * ff;
+                    gd.out = s.moe_y.as<float>(); gd.ld_out = width; gd.N = width; gd.K = ff;
+                    B2_TRY(linear_grouped_f32(gd, st));
+                    B2_TRY(moe_combine_f32(x, s.moe_y.as<float>(), width, pos, s.moe_w.as<float>(), R, top, width, rm, st));
+                } else {
+                    B2_TRY(lin(xn, width, W.up_w, d.ff, width, s.ff.as<float>(), (d.ff + 7) / 8 * 8, R, LIN_RELU_SQ));
+                    B2_TRY(lin(s.ff.as<float>(), (d.ff + 7) / 8 * 8, W.down_w, width, d.ff, x, width, R, LIN_NONE, rm, 1));
+                }
+            }
+            if (resid_out != nullptr)
+                B2_CUDA_CHECK(cudaMemcpyAsync(resid_out + ri * (size_t)R * width, x, (size_t)R * width * F4, cudaMemcpyDeviceToDevice, st));
+            continue;
+        }
+        if (pass >= 0) B2_TRY(rms_scalar_f32(x, nullptr, nullptr, pass_add, pass_vec, nullptr, R, width, eps, st));
         if (d.type == B2_MIXER_MAMBA2) {
             float* proj = s.proj.as<float>();
             const int gn = d.m_groups * d.m_state;
@@ -261,7 +396,33 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
             B2_TRY(layernorm_add_f32(x, mix, W.norm2.as<float>(), W.norm2_b.as<float>(), R, width, eps, st));
         }
         if (resid_out != nullptr)
-            B2_CUDA_CHECK(cudaMemcpyAsync(resid_out + li * (size_t)R * width, x, (size_t)R * width * F4, cudaMemcpyDeviceToDevice, st));
+            B2_CUDA_CHECK(cudaMemcpyAsync(resid_out + ri * (size_t)R * width, x, (size_t)R * width * F4, cudaMemcpyDeviceToDevice, st));
+    }
+    return 0;
+}
+
+// token rows -> x (and the kept copy x0 of a looped model); tokens are indexed by row
+static int seq_embed(b2_model* m, b2_kv* kv, const int32_t* tokens, int R, int nseg, cudaStream_t st) {
+    SeqModel& s = *m->seq;
+    if (s.d.bigram_buckets > 0 || s.x0.p != nullptr)
+        return embed_bigram_rows_f32(tokens, s.segs.as<SeqSeg>(), nseg, nseg == 1 ? R : 1, s.embed.p, s.bigram.p, s.w_dtype, kv->seq->last_tok.as<int32_t>(),
+                                     s.x.as<float>(), s.x0.as<float>(), s.d.width, s.d.vocab, s.d.bigram_buckets, s.d.bigram_mul_prev, s.d.bigram_mul_cur,
+                                     m->err_dev, st);
+    return embed_rows_f32(tokens, s.embed.p, s.w_dtype, s.x.as<float>(), R, s.d.width, s.d.vocab, m->err_dev, st);
+}
+
+// rows `index` (null: all) of x -> final norm -> head -> soft-cap: fp32 logits [n, vocab]
+static int seq_head(b2_model* m, const int32_t* index, int n, float* logits, int64_t ld, cudaStream_t st) {
+    SeqModel& s = *m->seq;
+    if (s.d.block == B2_BLOCK_PRE_RMS1)
+        B2_TRY(rms_scalar_f32(s.x.as<float>(), index, s.final_w.as<float>(), nullptr, nullptr, s.xn.as<float>(), n, s.d.width, s.d.norm_eps, st));
+    else
+        B2_TRY(layernorm_gather_f32(s.x.as<float>(), index, s.final_w.as<float>(), s.final_b.as<float>(), s.xn.as<float>(), n, s.d.width, s.d.norm_eps, st));
+    const Lin lin{m, st};
+    B2_TRY(lin(s.xn.as<float>(), s.d.width, s.head, s.d.vocab, s.d.width, logits, ld, n));
+    if (s.d.logit_softcap > 0.f) {
+        B2_CHECK_ARG(ld == s.d.vocab, "seq_head: soft-capped logits are contiguous rows");
+        B2_TRY(softcap_f32(logits, (size_t)n * s.d.vocab, s.d.logit_softcap, st));
     }
     return 0;
 }
@@ -271,11 +432,9 @@ int seq_decode_launch(b2_model* m, b2_kv* kv, int B, int slot0, cudaStream_t st)
     SeqModel& s = *m->seq;
     RowMap rm{s.segs.as<SeqSeg>(), s.row_slot.as<int32_t>(), s.row_pos.as<int32_t>()};
     B2_TRY(rowmap_decode(rm, kv->len_dev.as<int32_t>(), kv->sstate.as<SampleState>(), kv->rows_dev.as<RowState>(), slot0, B, st));
-    B2_TRY(embed_rows_f32(kv->tok.as<int32_t>() + slot0, s.embed.p, s.w_dtype, s.x.as<float>(), B, s.d.width, s.d.vocab, m->err_dev, st));
+    B2_TRY(seq_embed(m, kv, kv->tok.as<int32_t>() + slot0, B, B, st));
     B2_TRY(seq_forward(m, kv, B, B, nullptr, st));
-    B2_TRY(layernorm_gather_f32(s.x.as<float>(), nullptr, s.final_w.as<float>(), s.final_b.as<float>(), s.xn.as<float>(), B, s.d.width, s.d.norm_eps, st));
-    const Lin lin{m, st};
-    B2_TRY(lin(s.xn.as<float>(), s.d.width, s.head, s.d.vocab, s.d.width, m->logits.as<float>(), s.d.vocab, B));
+    B2_TRY(seq_head(m, nullptr, B, m->logits.as<float>(), s.d.vocab, st));
     B2_TRY(sample_publish(m->logits.as<float>(), s.d.vocab, B, kv->sstate.as<SampleState>(), kv->rows_dev.as<RowState>() + slot0,
                           kv->tok.as<int32_t>() + slot0, kv->out_tokens.as<int32_t>(), kv->step_counter.as<int32_t>(),
                           kv->len_dev.as<int32_t>() + slot0, kv->ring_dev, kv->ring_cap, SP_SELECT | SP_WRITE_OUT | SP_BUMP, 0, st));
@@ -291,6 +450,17 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     const std::string k(key);
     if (k == "embed") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.embed, WD, (size_t)V * width, 0, ptr, dt, (int64_t)V * width); }
     if (k == "head") { B2_TRY(want_shape(key, shape, ndim, V, width)); s.got[k] = 1; return put_tensor(s.head, WD, (size_t)((V + 7) / 8 * 8) * width, 0, ptr, dt, (int64_t)V * width); }
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1;
+    if (k == "final.norm" && pre) { B2_TRY(want_shape(key, shape, ndim, 1)); s.got[k] = 1; return put_tensor(s.final_w, DT_F32, 1, 0, ptr, dt, 1); }
+    if (k == "bigram" && s.d.bigram_buckets > 0) {
+        const int64_t rows = (int64_t)s.d.bigram_buckets + 1;
+        B2_TRY(want_shape(key, shape, ndim, rows, width)); s.got[k] = 1;
+        return put_tensor(s.bigram, WD, (size_t)rows * width, 0, ptr, dt, rows * width);
+    }
+    if (k == "loop.step" && s.d.loop_times > 1) {
+        B2_TRY(want_shape(key, shape, ndim, s.d.loop_times, width)); s.got[k] = 1;
+        return put_tensor(s.loop_step, DT_F32, (size_t)s.d.loop_times * width, 0, ptr, dt, (int64_t)s.d.loop_times * width);
+    }
     if (k == "final.norm") { B2_TRY(want_shape(key, shape, ndim, width)); s.got[k] = 1; return put_tensor(s.final_w, DT_F32, width, 0, ptr, dt, width); }
     if (k == "final.norm.b") { B2_TRY(want_shape(key, shape, ndim, width)); s.got[k] = 1; return put_tensor(s.final_b, DT_F32, width, 0, ptr, dt, width); }
     int li = -1, used = 0;
@@ -306,6 +476,86 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     auto vec = [&](DevBuf& b, int64_t n) -> int { B2_TRY(want_shape(key, shape, ndim, n)); W.got[r] = 1; return put_tensor(b, DT_F32, n, 0, ptr, dt, n); };
     // Linear weights are allocated with their rows padded to a multiple of 8 (zeros): the tensor-core GEMM wants N % 8 == 0
     auto mat = [&](DevBuf& b, int64_t o, int64_t i) -> int { B2_TRY(want_shape(key, shape, ndim, o, i)); W.got[r] = 1; return put_tensor(b, WD, (size_t)((o + 7) / 8 * 8) * i, 0, ptr, dt, o * i); };
+    if (pre) {
+        // a fused matrix of several projections that share their input: part j lands at its row offset
+        auto part = [&](DevBuf& b, int total_rows, int row0, int rows, int cols) -> int {
+            B2_TRY(want_shape(key, shape, ndim, rows, cols));
+            W.got[r] = 1;
+            return put_tensor(b, WD, (size_t)((total_rows + 7) / 8 * 8) * cols, (size_t)row0 * cols, ptr, dt, (int64_t)rows * cols);
+        };
+        if (r == "norm1") return vec(W.norm1, 1);
+        if (r == "norm2" && d.ff > 0) return vec(W.norm2, 1);
+        if (d.type == B2_MIXER_LATENT_ATTN) {
+            const int H = d.la_heads, dk = d.la_dim, dv = d.la_vdim, rank = d.la_rank;
+            if (r == "mix.q") return part(W.qdg_w, L.pproj, 0, L.pq, width);
+            if (r == "mix.dkv") return part(W.qdg_w, L.pproj, L.pq, rank, width);
+            if (r == "mix.g") return part(W.qdg_w, L.pproj, L.pq + rank, H, width);
+            if (r == "mix.dkv.norm") return vec(W.dkv_norm, rank);
+            if (r == "mix.sink") return vec(W.sink, H);
+            if (r == "mix.uv") return mat(W.uv_w, (int64_t)H * dv, rank);
+            if (r == "mix.o") return mat(W.o_w, width, (int64_t)H * dv);
+            if (r == "mix.uk") {
+                // stored per head as [rank][dim]: the query is carried into the latent space by a Linear with this matrix
+                B2_TRY(want_shape(key, shape, ndim, (int64_t)H * dk, rank));
+                DevBuf tmp;
+                B2_TRY(put_tensor(tmp, WD, (size_t)H * dk * rank, 0, ptr, dt, (int64_t)H * dk * rank));
+                int rc = W.ukT.alloc(((size_t)H * rank + 8) * dk * esz(WD));
+                if (rc == 0) rc = cudaMemset(W.ukT.p, 0, W.ukT.bytes) == cudaSuccess ? 0 : -2;
+                if (rc == 0) rc = transpose_blocks(tmp.p, W.ukT.p, H, dk, rank, (int)esz(WD), 0);
+                cudaStreamSynchronize(0);
+                tmp.free();
+                W.got[r] = 1;
+                return rc;
+            }
+        } else if (d.type == B2_MIXER_HGRN2) {
+            const int H = d.g_heads, dk = d.g_dim, dv = d.g_vdim;
+            if (r == "mix.q") return part(W.qfv_w, L.pproj, 0, L.pq, width);
+            if (r == "mix.f") return part(W.qfv_w, L.pproj, L.pq, L.pq, width);
+            if (r == "mix.v") return part(W.qfv_w, L.pproj, 2 * L.pq, H * dv, width);
+            if (r == "mix.f.b") return vec(W.f_b, (int64_t)H * dk);
+            if (r == "mix.lower") return vec(W.lower, (int64_t)H * dk);
+            if (r == "mix.norm") return vec(W.hnorm, dv);
+            if (r == "mix.o") return mat(W.o_w, width, (int64_t)H * dv);
+        }
+        if (d.ff > 0 && d.ff_kind == B2_FF_POLYNORM) {
+            if (r == "mlp.up") return mat(W.up_w, d.ff, width);
+            if (r == "mlp.down") return mat(W.down_w, width, d.ff);
+            if (r == "mlp.up.b") return vec(W.up_b, d.ff);
+            if (r == "mlp.act") return vec(W.act_coef, 4);
+            if (r == "mlp.down.b") {
+                B2_TRY(vec(W.down_b, width));
+                return put_tensor(W.down_b16, DT_BF16, (size_t)(width + 7) / 8 * 8, 0, ptr, dt, width);
+            }
+        } else if (d.ff > 0 && d.ff_kind == B2_FF_MOE) {
+            const int E = d.moe_experts, ff = d.ff, sf = d.moe_shared_ff;
+            if (r == "mlp.router") return mat(W.router_w, E, width);
+            if (sf > 0) {
+                if (r == "mlp.shared.gate") return part(W.sgu_w, 2 * sf, 0, sf, width);
+                if (r == "mlp.shared.up") return part(W.sgu_w, 2 * sf, sf, sf, width);
+                if (r == "mlp.shared.down") return mat(W.sd_w, width, sf);
+            }
+            int e = -1, eu = 0;
+            if (sscanf(r.c_str(), "mlp.e%d.%n", &e, &eu) == 1 && eu > 0 && e >= 0 && e < E) {
+                const std::string which = r.substr(eu);
+                // experts side by side: [E][gate | up][width] and [E][width][ff] (8 spare rows behind the last one)
+                if (which == "gate" || which == "up") {
+                    B2_TRY(want_shape(key, shape, ndim, ff, width));
+                    W.got[r] = 1;
+                    return put_tensor(W.egu_w, WD, ((size_t)E * 2 * ff + 8) * width, ((size_t)e * 2 + (which == "up")) * ff * width, ptr, dt, (int64_t)ff * width);
+                }
+                if (which == "down") {
+                    B2_TRY(want_shape(key, shape, ndim, width, ff));
+                    W.got[r] = 1;
+                    return put_tensor(W.ed_w, WD, ((size_t)E * width + 8) * ff, (size_t)e * width * ff, ptr, dt, (int64_t)width * ff);
+                }
+            }
+        } else if (d.ff > 0) {
+            if (r == "mlp.up") return mat(W.up_w, d.ff, width);
+            if (r == "mlp.down") return mat(W.down_w, width, d.ff);
+        }
+        set_error("set_weight: tensor '%s' does not belong to a layer of this kind", key);
+        return -1;
+    }
     if (r == "norm1") return vec(W.norm1, width);
     if (r == "norm1.b") return vec(W.norm1_b, width);
     if (d.ff > 0) {
@@ -360,7 +610,23 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
     return -1;
 }
 
-static std::vector<std::string> required_of(const SeqLayerInfo& L) {
+static std::vector<std::string> required_of(const SeqLayerInfo& L, bool pre) {
+    if (pre) {
+        std::vector<std::string> v = {"norm1", "mix.q", "mix.o"};
+        if (L.d.type == B2_MIXER_LATENT_ATTN) for (const char* n : {"mix.dkv", "mix.dkv.norm", "mix.uk", "mix.uv", "mix.sink", "mix.g"}) v.push_back(n);
+        else for (const char* n : {"mix.f", "mix.f.b", "mix.lower", "mix.v", "mix.norm"}) v.push_back(n);
+        if (L.d.ff > 0) {
+            v.push_back("norm2");
+            if (L.d.ff_kind == B2_FF_POLYNORM) for (const char* n : {"mlp.up", "mlp.up.b", "mlp.down", "mlp.down.b", "mlp.act"}) v.push_back(n);
+            else if (L.d.ff_kind == B2_FF_MOE) {
+                v.push_back("mlp.router");
+                for (int e = 0; e < L.d.moe_experts; ++e)
+                    for (const char* n : {"gate", "up", "down"}) v.push_back("mlp.e" + std::to_string(e) + "." + n);
+                if (L.d.moe_shared_ff > 0) for (const char* n : {"mlp.shared.gate", "mlp.shared.up", "mlp.shared.down"}) v.push_back(n);
+            } else for (const char* n : {"mlp.up", "mlp.down"}) v.push_back(n);
+        }
+        return v;
+    }
     std::vector<std::string> v = {"norm1", "norm1.b"};
     if (L.d.ff > 0) for (const char* n : {"norm2", "norm2.b", "mlp.up", "mlp.down"}) v.push_back(n);
     if (L.d.type == B2_MIXER_MAMBA2) {
@@ -377,11 +643,16 @@ static std::vector<std::string> required_of(const SeqLayerInfo& L) {
 int seq_finalize(b2_model* m) {
     SeqModel& s = *m->seq;
     std::string missing;
-    for (const char* n : {"embed", "head", "final.norm", "final.norm.b"})
+    const bool pre = s.d.block == B2_BLOCK_PRE_RMS1;
+    std::vector<std::string> top = {"embed", "head", "final.norm"};
+    if (!pre) top.push_back("final.norm.b");
+    if (s.d.bigram_buckets > 0) top.push_back("bigram");
+    if (s.d.loop_times > 1) top.push_back("loop.step");
+    for (const std::string& n : top)
         if (!s.got.count(n) && missing.size() < 600) { missing += n; missing += ' '; }
     for (size_t i = 0; i < s.layers.size(); ++i) {
         if (s.layers[i].src != (int)i) continue;
-        for (const std::string& n : required_of(s.layers[i]))
+        for (const std::string& n : required_of(s.layers[i], pre))
             if (!s.w[i].got.count(n) && missing.size() < 600) missing += "l" + std::to_string(i) + "." + n + " ";
     }
     if (!missing.empty()) {
@@ -390,14 +661,23 @@ int seq_finalize(b2_model* m) {
     }
     const int width = s.d.width;
     int pw = 1, aw = 1, yw = 1, rw = 1, kw = 1, fw = 1;
+    int latw = 0, moe_top = 0, moe_e = 0, moe_ff = 0;
     for (const SeqLayerInfo& L : s.layers) {
         if (L.d.type == B2_MIXER_MAMBA2) {
             pw = std::max(pw, L.dproj_ld); aw = std::max(aw, L.conv_ch); yw = std::max(yw, L.inner);
-        } else {
+        } else if (L.d.type == B2_MIXER_PARALLEL) {
             pw = std::max(pw, L.lproj_ld); yw = std::max(yw, std::max(L.ng, L.rn)); rw = std::max(rw, L.rn); kw = std::max(kw, L.d.r_decay_rank);
+        } else {
+            pw = std::max(pw, L.pproj_ld); yw = std::max(yw, L.pv);
+            if (L.d.type == B2_MIXER_LATENT_ATTN) latw = std::max(latw, L.d.la_heads * L.d.la_rank);
         }
-        fw = std::max(fw, L.d.ff);
+        fw = std::max(fw, (L.d.ff + 7) / 8 * 8);
+        if (L.d.ff > 0 && L.d.ff_kind == B2_FF_MOE) {
+            fw = std::max(fw, (2 * L.d.moe_shared_ff + 7) / 8 * 8);
+            moe_top = std::max(moe_top, L.d.moe_top); moe_e = std::max(moe_e, L.d.moe_experts); moe_ff = std::max(moe_ff, L.d.ff);
+        }
     }
+    pw = std::max(pw, (moe_e + 7) / 8 * 8);
     s.proj_w = pw; s.act_w = aw; s.y_w = yw; s.rp_w = rw; s.rank_w = kw; s.ff_w = fw;
     const size_t R = (size_t)s.rows;
     B2_TRY(s.x.alloc(R * width * F4));
@@ -412,9 +692,33 @@ int seq_finalize(b2_model* m) {
     B2_TRY(s.wlog.alloc(R * rw * F4));
     B2_TRY(s.ff.alloc(R * fw * F4));
     B2_TRY(s.xn.alloc(R * width * F4));
+    if (pre) B2_TRY(s.ffa.alloc(R * fw * F4));
+    if (s.d.loop_times > 1) B2_TRY(s.x0.alloc(R * width * F4));
+    if (latw > 0) {
+        s.lat_w = latw;
+        B2_TRY(s.qabs.alloc(R * latw * F4));
+        B2_TRY(s.olat.alloc(R * latw * F4));
+    }
+    if (moe_e > 0) {
+        // (token, choice) pairs sorted by expert, every expert padded to whole tiles
+        s.moe_top = moe_top; s.moe_e = moe_e;
+        s.moe_tiles = (int)((R * moe_top + (size_t)moe_e * (GROUPED_TILE_ROWS - 1) + GROUPED_TILE_ROWS - 1) / GROUPED_TILE_ROWS);
+        s.moe_rows = s.moe_tiles * GROUPED_TILE_ROWS;
+        const size_t P = (size_t)s.moe_rows;
+        B2_TRY(s.rlogit.alloc(R * ((moe_e + 7) / 8 * 8) * F4));
+        B2_TRY(s.moe_idx.alloc(R * moe_top * 4));
+        B2_TRY(s.moe_w.alloc(R * moe_top * F4));
+        B2_TRY(s.moe_pos.alloc(R * moe_top * 4));
+        B2_TRY(s.moe_src.alloc(P * 4));
+        B2_TRY(s.moe_tile.alloc((size_t)s.moe_tiles * 4));
+        B2_TRY(s.moe_h.alloc(P * 2 * moe_ff * F4));
+        B2_TRY(s.moe_a.alloc(P * moe_ff * F4));
+        B2_TRY(s.moe_y.alloc(P * width * F4));
+    }
     {
         int kmax = width;
-        for (const SeqLayerInfo& L : s.layers) kmax = std::max(kmax, std::max(std::max(L.inner, L.ng), std::max(L.rn, L.d.ff)));
+        for (const SeqLayerInfo& L : s.layers)
+            kmax = std::max(kmax, std::max(std::max(std::max(L.inner, L.ng), std::max(L.rn, L.d.ff)), std::max(std::max(L.pv, L.d.la_rank), std::max(L.d.la_dim, L.d.moe_shared_ff))));
         s.a16_w = (kmax + 7) / 8 * 8;
         if (s.d.compute == B2_COMPUTE_BF16) B2_TRY(s.a16.alloc(R * s.a16_w * 2));
     }
@@ -433,11 +737,13 @@ void seq_model_free(b2_model* m) {
     for (SeqWeights& W : s.w) {
         DevBuf* bs[] = {&W.norm1, &W.norm1_b, &W.norm2, &W.norm2_b, &W.in_w, &W.conv_w, &W.conv_b, &W.dt_bias, &W.a_log, &W.skip, &W.mnorm, &W.o_w,
                         &W.lproj_w, &W.rel, &W.lo_w, &W.mu, &W.r_w, &W.k_w, &W.v_w, &W.g_w, &W.w1, &W.w2, &W.w0, &W.bonus, &W.rnorm, &W.ro_w,
-                        &W.up_w, &W.down_w};
+                        &W.up_w, &W.down_w, &W.qdg_w, &W.dkv_norm, &W.ukT, &W.uv_w, &W.sink, &W.qfv_w, &W.f_b, &W.lower, &W.hnorm, &W.up_b, &W.down_b,
+                        &W.down_b16, &W.act_coef, &W.router_w, &W.egu_w, &W.ed_w, &W.sgu_w, &W.sd_w};
         for (DevBuf* b : bs) b->free();
     }
     DevBuf* bs[] = {&s.embed, &s.head, &s.final_w, &s.final_b, &s.x, &s.proj, &s.act, &s.y, &s.gated, &s.mixout, &s.mixes, &s.rp, &s.wl1, &s.wlog,
-                    &s.ff, &s.xn, &s.tok, &s.want, &s.segs, &s.row_slot, &s.row_pos, &s.a16};
+                    &s.ff, &s.xn, &s.tok, &s.want, &s.segs, &s.row_slot, &s.row_pos, &s.a16, &s.bigram, &s.loop_step, &s.x0, &s.qabs, &s.olat, &s.ffa,
+                    &s.rlogit, &s.moe_idx, &s.moe_w, &s.moe_pos, &s.moe_src, &s.moe_tile, &s.moe_h, &s.moe_a, &s.moe_y};
     for (DevBuf* b : bs) b->free();
     delete m->seq;
     m->seq = nullptr;
@@ -456,12 +762,16 @@ static int distance_bucket(int n, int rows, double far_) {
 
 int64_t seq_kv_bytes(const b2_model* m, int B, int Smax) {
     int64_t n = 0;
-    for (const SeqLayerInfo& L : m->seq->layers) {
+    for (const SeqRun& run : m->seq->runs) {
+        const SeqLayerInfo& L = m->seq->layers[run.layer];
         const b2_seq_layer_desc& d = L.d;
         if (d.type == B2_MIXER_MAMBA2) n += (int64_t)B * d.m_heads * d.m_state * d.m_vdim + (int64_t)B * (d.m_conv - 1) * L.conv_ch;
-        else n += (int64_t)B * d.a_kv_heads * Smax * (d.a_dim + d.a_vdim) + (int64_t)B * d.r_heads * d.r_dim * d.r_dim + (int64_t)B * m->seq->d.width;
+        else if (d.type == B2_MIXER_PARALLEL)
+            n += (int64_t)B * d.a_kv_heads * Smax * (d.a_dim + d.a_vdim) + (int64_t)B * d.r_heads * d.r_dim * d.r_dim + (int64_t)B * m->seq->d.width;
+        else if (d.type == B2_MIXER_LATENT_ATTN) n += (int64_t)B * Smax * d.la_rank;
+        else n += (int64_t)B * d.g_heads * d.g_dim * d.g_vdim;
     }
-    return n * 4;
+    return n * 4 + (m->seq->d.bigram_buckets > 0 ? (int64_t)B * 4 : 0);
 }
 
 int seq_kv_alloc(b2_kv* kv) {
@@ -469,13 +779,23 @@ int seq_kv_alloc(b2_kv* kv) {
     const SeqModel& s = *m->seq;
     const size_t B = kv->max_batch, Smax = kv->max_seq;
     kv->seq = new SeqState();
-    kv->seq->layer.resize(s.layers.size());
+    kv->seq->layer.resize(s.runs.size());
+    B2_TRY(kv->seq->last_tok.alloc(B * 4));
+    cudaMemset(kv->seq->last_tok.p, 0, B * 4);
     int maxH = 1, maxdv = 1;
-    for (size_t li = 0; li < s.layers.size(); ++li) {
-        const SeqLayerInfo& L = s.layers[li];
+    for (size_t li = 0; li < s.runs.size(); ++li) {
+        const SeqLayerInfo& L = s.layers[s.runs[li].layer];
         const b2_seq_layer_desc& d = L.d;
         SeqLayerState& S = kv->seq->layer[li];
-        if (d.type == B2_MIXER_MAMBA2) {
+        if (d.type == B2_MIXER_LATENT_ATTN) {
+            B2_TRY(S.lat.alloc(B * Smax * d.la_rank * F4));
+            cudaMemset(S.lat.p, 0, S.lat.bytes);
+            maxH = std::max(maxH, d.la_heads);
+            maxdv = std::max(maxdv, d.la_rank);
+        } else if (d.type == B2_MIXER_HGRN2) {
+            B2_TRY(S.gla.alloc(B * d.g_heads * d.g_dim * d.g_vdim * F4));
+            cudaMemset(S.gla.p, 0, S.gla.bytes);
+        } else if (d.type == B2_MIXER_MAMBA2) {
             B2_TRY(S.ssm.alloc(B * d.m_heads * d.m_state * d.m_vdim * F4));
             B2_TRY(S.conv_tail.alloc(std::max<size_t>(1, B * (d.m_conv - 1) * L.conv_ch) * F4));
             cudaMemset(S.ssm.p, 0, S.ssm.bytes);
@@ -505,9 +825,10 @@ int seq_kv_alloc(b2_kv* kv) {
 void seq_kv_free(b2_kv* kv) {
     if (kv->seq == nullptr) return;
     for (SeqLayerState& S : kv->seq->layer) {
-        DevBuf* bs[] = {&S.ssm, &S.conv_tail, &S.kc, &S.vc, &S.bucket_of, &S.wkv, &S.prev};
+        DevBuf* bs[] = {&S.ssm, &S.conv_tail, &S.kc, &S.vc, &S.bucket_of, &S.wkv, &S.prev, &S.lat, &S.gla};
         for (DevBuf* b : bs) b->free();
     }
+    kv->seq->last_tok.free();
     kv->seq->attn_partial.free();
     delete kv->seq;
     kv->seq = nullptr;
@@ -529,6 +850,8 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
     B2_CHECK_ARG(d.compute == B2_COMPUTE_BF16 || d.compute == B2_COMPUTE_F32, "b2_seq_model_create: unknown compute mode %d", d.compute);
     B2_CHECK_ARG(d.max_batch >= 1 && d.max_rows >= 1, "b2_seq_model_create: bad workspace sizing");
     B2_CHECK_ARG(d.norm_eps >= 0.f, "b2_seq_model_create: negative eps");
+    B2_CHECK_ARG(d.block == B2_BLOCK_POST_LN || d.block == B2_BLOCK_PRE_RMS1, "b2_seq_model_create: unknown block form %d", d.block);
+    B2_CHECK_ARG(d.bigram_buckets >= 0 && d.logit_softcap >= 0.f, "b2_seq_model_create: negative bigram buckets or soft-cap");
     SeqModel* s = new SeqModel();
     s->d = d;
     s->w_dtype = d.compute == B2_COMPUTE_F32 ? DT_F32 : DT_BF16;
@@ -574,8 +897,29 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             L.lproj = L.nq + L.nk + L.nv + L.ng;
             L.lproj_ld = (L.lproj + 7) / 8 * 8;
             L.rn = l.r_heads * l.r_dim;
+        } else if (l.type == B2_MIXER_LATENT_ATTN) {
+            if (l.la_heads < 1 || l.la_dim < 1 || l.la_vdim < 1) why = "latent attention: heads and head sizes must be positive";
+            else if (l.la_rank < 1 || l.la_rank > 512) why = "latent attention: latent size 1..512";
+            L.pq = l.la_heads * l.la_dim; L.pv = l.la_heads * l.la_vdim;
+            L.pproj = L.pq + l.la_rank + l.la_heads;
+            L.pproj_ld = (L.pproj + 7) / 8 * 8;
+        } else if (l.type == B2_MIXER_HGRN2) {
+            if (l.g_heads < 1 || l.g_dim < 1 || l.g_dim > 256 || l.g_vdim < 1) why = "hgrn2: heads, dim 1..256, vdim";
+            L.pq = l.g_heads * l.g_dim; L.pv = l.g_heads * l.g_vdim;
+            L.pproj = 2 * L.pq + L.pv;
+            L.pproj_ld = (L.pproj + 7) / 8 * 8;
         } else {
             why = "unknown mixer type";
+        }
+        const bool pre_mixer = l.type == B2_MIXER_LATENT_ATTN || l.type == B2_MIXER_HGRN2;
+        if (why == nullptr && pre_mixer != (d.block == B2_BLOCK_PRE_RMS1)) why = "this mixer does not go with the model's block form";
+        if (why == nullptr && l.ff > 0) {
+            if (l.ff_kind != B2_FF_RELU_SQ && d.block != B2_BLOCK_PRE_RMS1) why = "this feed-forward needs the pre-norm block";
+            else if (l.ff_kind == B2_FF_MOE) {
+                if (l.moe_experts < 1 || l.moe_top < 1 || l.moe_top > 32 || l.moe_top > l.moe_experts) why = "moe: experts >= top >= 1, at most 32 choices";
+                else if (l.moe_groups < 1 || l.moe_experts % l.moe_groups || l.moe_keep < 1 || l.moe_keep > l.moe_groups) why = "moe: groups must divide experts, 1 <= keep <= groups";
+                else if (l.moe_shared_ff < 0) why = "moe: negative shared width";
+            } else if (l.ff_kind != B2_FF_RELU_SQ && l.ff_kind != B2_FF_POLYNORM) why = "unknown feed-forward kind";
         }
         if (why == nullptr && L.src != i) {
             b2_seq_layer_desc a = l, b = s->layers[L.src].d;
@@ -588,6 +932,24 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
             return -1;
         }
     }
+    // layer runs: the layers in order, the looped block `times` times in a row
+    {
+        const bool looped = d.loop_times > 1;
+        if (looped && !(d.loop_start >= 0 && d.loop_start < d.loop_stop && d.loop_stop <= d.n_layers)) {
+            set_error("b2_seq_model_create: loop [%d, %d) x %d does not fit %d layers", d.loop_start, d.loop_stop, d.loop_times, d.n_layers);
+            delete s;
+            return -1;
+        }
+        for (int i = 0; i < d.n_layers; ++i) {
+            if (looped && i == d.loop_start) {
+                for (int t = 0; t < d.loop_times; ++t)
+                    for (int j = d.loop_start; j < d.loop_stop; ++j) s->runs.push_back(SeqRun{j, j == d.loop_start ? t : -1});
+                i = d.loop_stop - 1;
+            } else {
+                s->runs.push_back(SeqRun{i, -1});
+            }
+        }
+    }
     b2_model* m = new b2_model();
     memset(&m->d, 0, sizeof(m->d));
     m->d.vocab = d.vocab; m->d.max_batch = d.max_batch; m->d.max_seq = d.max_rows; m->d.layers = d.n_layers; m->d.hidden = d.width;
@@ -596,6 +958,10 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
     cudaGetDevice(&m->device);
     *out = m;
     return 0;
+}
+
+int b2_seq_model_runs(const b2_model* m) {
+    return (m != nullptr && m->arch == B2_ARCH_LAYER_LIST) ? (int)m->seq->runs.size() : -1;
 }
 
 int b2_append_tokens(b2_model* m, b2_kv* kv, int slot, const int32_t* tokens_host, int n, int restart, const int32_t* want_host, int n_want,
@@ -617,24 +983,21 @@ int b2_append_tokens(b2_model* m, b2_kv* kv, int slot, const int32_t* tokens_hos
     RowMap rm{s.segs.as<SeqSeg>(), s.row_slot.as<int32_t>(), s.row_pos.as<int32_t>()};
     // a slot that starts over begins from position 0 whatever its device-side length says
     B2_TRY(rowmap_portion(rm, kv->len_dev.as<int32_t>(), slot, n, start == 0 ? 1 : 0, st));
-    B2_TRY(embed_rows_f32(s.tok.as<int32_t>(), s.embed.p, s.w_dtype, s.x.as<float>(), n, s.d.width, s.d.vocab, m->err_dev, st));
+    B2_TRY(seq_embed(m, kv, s.tok.as<int32_t>(), n, 1, st));
     B2_TRY(seq_forward(m, kv, n, 1, resid_out, st));
     if (n_want > 0) {
         B2_CUDA_CHECK(cudaMemcpyAsync(s.want.p, want_host, (size_t)n_want * 4, cudaMemcpyHostToDevice, st));
-        B2_TRY(layernorm_gather_f32(s.x.as<float>(), s.want.as<int32_t>(), s.final_w.as<float>(), s.final_b.as<float>(), s.xn.as<float>(), n_want,
-                                    s.d.width, s.d.norm_eps, st));
-        const Lin lin{m, st};
         cudaPointerAttributes attr;
         bool dev_out = cudaPointerGetAttributes(&attr, logits_out) == cudaSuccess && (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged);
         cudaGetLastError();
         if (dev_out) {
-            B2_TRY(lin(s.xn.as<float>(), s.d.width, s.head, s.d.vocab, s.d.width, logits_out, s.d.vocab, n_want));
+            B2_TRY(seq_head(m, s.want.as<int32_t>(), n_want, logits_out, s.d.vocab, st));
         } else {
             // host destination: through the projection workspace, in pieces of what it holds
             const int per = (int)std::max<size_t>(1, ((size_t)s.rows * s.proj_w) / s.d.vocab);
             for (int i0 = 0; i0 < n_want; i0 += per) {
                 const int c = std::min(per, n_want - i0);
-                B2_TRY(lin(s.xn.as<float>() + (size_t)i0 * s.d.width, s.d.width, s.head, s.d.vocab, s.d.width, s.proj.as<float>(), s.d.vocab, c));
+                B2_TRY(seq_head(m, s.want.as<int32_t>() + i0, c, s.proj.as<float>(), s.d.vocab, st));
                 B2_CUDA_CHECK(cudaMemcpyAsync(logits_out + (size_t)i0 * s.d.vocab, s.proj.p, (size_t)c * s.d.vocab * 4, cudaMemcpyDeviceToHost, st));
                 B2_CUDA_CHECK(cudaStreamSynchronize(st));
             }

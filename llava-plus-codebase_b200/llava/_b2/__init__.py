@@ -62,16 +62,25 @@ class SeqLayerDesc(_c.Structure):
                 ("a_rel_rows", _c.c_int32), ("a_bias_max", _c.c_float), ("a_scale", _c.c_float), ("a_softcap", _c.c_float),
                 ("a_temp_coef", _c.c_float), ("a_temp_every", _c.c_float),
                 ("r_heads", _c.c_int32), ("r_dim", _c.c_int32), ("r_decay_rank", _c.c_int32),
-                ("left_scale", _c.c_float), ("right_scale", _c.c_float)]
+                ("left_scale", _c.c_float), ("right_scale", _c.c_float),
+                ("ff_kind", _c.c_int32), ("moe_experts", _c.c_int32), ("moe_top", _c.c_int32), ("moe_groups", _c.c_int32),
+                ("moe_keep", _c.c_int32), ("moe_shared_ff", _c.c_int32), ("moe_scale", _c.c_float),
+                ("la_heads", _c.c_int32), ("la_dim", _c.c_int32), ("la_vdim", _c.c_int32), ("la_rank", _c.c_int32), ("la_scale", _c.c_float),
+                ("g_heads", _c.c_int32), ("g_dim", _c.c_int32), ("g_vdim", _c.c_int32)]
 
 
 class SeqModelDesc(_c.Structure):
     """b2_seq_model_desc (include/b2llava.h)."""
     _fields_ = [("width", _c.c_int32), ("vocab", _c.c_int32), ("n_layers", _c.c_int32), ("compute", _c.c_int32),
-                ("norm_eps", _c.c_float), ("max_batch", _c.c_int32), ("max_rows", _c.c_int32)]
+                ("norm_eps", _c.c_float), ("max_batch", _c.c_int32), ("max_rows", _c.c_int32),
+                ("block", _c.c_int32), ("residual_mult", _c.c_float), ("logit_softcap", _c.c_float),
+                ("bigram_buckets", _c.c_int32), ("bigram_mul_prev", _c.c_int32), ("bigram_mul_cur", _c.c_int32),
+                ("loop_start", _c.c_int32), ("loop_stop", _c.c_int32), ("loop_times", _c.c_int32)]
 
 
-MIXER_MAMBA2, MIXER_PARALLEL = 1, 2
+MIXER_MAMBA2, MIXER_PARALLEL, MIXER_LATENT_ATTN, MIXER_HGRN2 = 1, 2, 3, 4
+FF_RELU_SQ, FF_POLYNORM, FF_MOE = 0, 1, 2
+BLOCK_POST_LN, BLOCK_PRE_RMS1 = 0, 1
 COMPUTE_BF16, COMPUTE_F32 = 0, 1
 
 
@@ -118,6 +127,7 @@ SIGNATURES = {
     "b2_decode_step_slots": (_i32, [_vp, _vp, _vp, _i32, _i32, _vp, _vp, _vp]),
     "b2_kv_free_slot": (_i32, [_vp, _i32, _vp]),
     "b2_kv_bytes": (_i64, [_vp, _i32, _i32]),
+    "b2_seq_model_runs": (_i32, [_vp]),
     "b2_op_gemm": (_i32, [_vp, _i32, _vp, _i32, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b2_op_gemv": (_i32, [_vp, _i64, _vp, _i32, _vp, _f32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b2_op_gemm_skinny": (_i32, [_vp, _i32, _vp, _i32, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp]),
@@ -472,6 +482,7 @@ class SeqEngine(Engine):
             check(self.lib.b2_seq_model_create(ctypes.byref(self.desc), self.layer_descs, ctypes.byref(h)), "b2_seq_model_create")
         self.handle = h
         self.hidden, self.vocab = model_desc["width"], model_desc["vocab"]
+        self.n_runs = int(self.lib.b2_seq_model_runs(self.handle))
         self.finalized = False
         self._kvs = weakref.WeakSet()
 
@@ -480,14 +491,14 @@ class SeqEngine(Engine):
 
     def append_tokens(self, kv, slot, tokens, want=(), restart=False, residuals=False):
         """Feed the next tokens of the request in `slot`; returns fp32 logits [len(want), vocab] on the device for the
-        positions `want` (indices into `tokens`), and with residuals=True also the residual stream after every layer
-        [layers, n, width]."""
+        positions `want` (indices into `tokens`), and with residuals=True also the residual stream after every layer run
+        [layer runs, n, width]."""
         toks = [int(t) for t in tokens]
         n, nw = len(toks), len(want)
         ctoks = (_c.c_int32 * n)(*toks)
         cwant = (_c.c_int32 * max(nw, 1))(*[int(w) for w in want])
         logits = torch.empty(nw, self.vocab, dtype=torch.float32, device=self.device) if nw else None
-        resid = torch.empty(self.desc.n_layers, n, self.hidden, dtype=torch.float32, device=self.device) if residuals else None
+        resid = torch.empty(self.n_runs, n, self.hidden, dtype=torch.float32, device=self.device) if residuals else None
         with torch.cuda.device(self.index):
             check(self.lib.b2_append_tokens(self.handle, kv.handle, int(slot), ctoks, n, int(bool(restart)), cwant, nw, ptr(logits),
                                             ptr(resid), stream_ptr()), "b2_append_tokens")

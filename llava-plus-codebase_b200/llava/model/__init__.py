@@ -10,11 +10,14 @@ import os
 MODEL_REGISTRY = {
     "llava": ("language_model.llava_llama", "LlavaLlamaForCausalLM"),
     "Katadra": ("language_model.katadra", "KatadraForCausalLM"),
+    "Pefivik": ("language_model.pefivik", "PefivikForCausalLM"),
 }
 _LAZY = {"LlavaLlamaForCausalLM": "language_model.llava_llama", "LlavaConfig": "language_model.llava_llama",
-         "KatadraForCausalLM": "language_model.katadra", "KatadraConfig": "language_model.katadra"}
+         "KatadraForCausalLM": "language_model.katadra", "KatadraConfig": "language_model.katadra",
+         "PefivikForCausalLM": "language_model.pefivik", "PefivikConfig": "language_model.pefivik"}
 
-__all__ = ["LlavaConfig", "LlavaLlamaForCausalLM", "KatadraConfig", "KatadraForCausalLM", "MODEL_REGISTRY", "model_class_for"]
+__all__ = ["LlavaConfig", "LlavaLlamaForCausalLM", "KatadraConfig", "KatadraForCausalLM", "PefivikConfig", "PefivikForCausalLM", "MODEL_REGISTRY",
+           "model_class_for"]
 
 
 def __getattr__(name):
