@@ -30,6 +30,7 @@ for p in (ROOT, os.path.join(ROOT, "llava-plus-codebase_b200"), os.path.join(ROO
 os.environ.setdefault("TRANSFORMERS_OFFLINE", "1")
 os.environ.setdefault("HF_HUB_OFFLINE", "1")
 
+import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 MODELS = {
@@ -54,11 +55,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the side measurements of the other BASELINE configs")
-    ap.add_argument("--arch", default="llava", choices=["llava", "katadra"],
+    ap.add_argument("--arch", default="llava", choices=["llava", "katadra", "pefivik"],
                     help="katadra: prefill / decode throughput of the layer-list decoder beside the LLaMA decoder of equal width, "
                          "depth and parameter count (random weights); the default workload and its JSON line are unchanged")
-    ap.add_argument("--widths", default="2048,4096", help="--arch katadra: model widths to measure")
-    ap.add_argument("--ctx", type=int, default=2048, help="--arch katadra: prompt length")
+    ap.add_argument("--widths", default="2048,4096", help="--arch katadra / pefivik: model widths to measure")
+    ap.add_argument("--ctx", type=int, default=2048, help="--arch katadra / pefivik: prompt length")
     return ap.parse_args()
 
 
@@ -770,6 +771,111 @@ def timed(fn, steps, warmup, flush):
     return ts[len(ts) // 2]
 
 
+def measure_layer_list(model, args, S, N, flush, pk, params, params_read):
+    """Prefill of S tokens and N decode steps at 1 and 8 slots of a layer-list model. `params`: matmul parameters a token
+    multiplies with (FLOPs / 2); params_read(B): parameters a decode step of B slots has to read."""
+    dev = model.device
+    eng = model._ensure_engine()
+    kv = eng.new_kv(8, S + N + 8)
+    toks = torch.randint(0, model.config.vocab, (S,)).tolist()
+    t_pre = timed(lambda: eng.append_tokens(kv, 0, toks, [S - 1], restart=True), args.steps, args.warmup, flush)
+    res = {"params_matmul": int(params), "prefill_ms": round(t_pre, 3), "prefill_tok_s": round(S / t_pre * 1e3, 1),
+           "prefill_frac_bf16_peak": round(2.0 * params * S / (t_pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+           "state_bytes_per_slot": eng.kv_bytes(1, S)}
+    for B in (1, 8):
+        for b in range(B):
+            eng.append_tokens(kv, b, toks, [], restart=True)
+        first = torch.zeros(B, dtype=torch.int32, device=dev)
+        eng.decode_greedy(kv, first, 4)                                   # eager step + graph capture
+        for b in range(B):
+            eng.append_tokens(kv, b, toks, [], restart=True)
+        t = timed(lambda: eng.decode_greedy(kv, first, N), 1, 0, flush) / N
+        moved = 2.0 * params_read(B) + B * eng.kv_bytes(1, S)             # weights once + every slot's state and key/value rows
+        res[f"decode_b{B}_ms_per_step"] = round(t, 4)
+        res[f"decode_b{B}_tok_s"] = round(B / t * 1e3, 1)
+        res[f"decode_b{B}_frac_hbm_peak"] = round(moved / (t * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
+    model.invalidate_engine()
+    return res
+
+
+def pefivik_config(width):
+    """Four layers of the sizes a model of this width would have: latent attention (heads of 128, latent 512) and HGRN2 (heads of
+    128) mixers, a PolyNorm feed-forward of 4 x width and a 16-expert mixture (top 2 of the best 2 of 4 groups, expert width
+    width / 4, a shared expert of width / 2)."""
+    heads = width // 128
+    lat = {"type": "latent_attention", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5}}
+    hg = {"type": "hgrn2", "mixer": {"heads": heads, "dim": 128, "vdim": 128}}
+    dense = {"kind": "dense", "ff": 4 * width}
+    moe = {"kind": "moe", "expert": {"ff": width // 4}, "shared": {"ff": width // 2},
+           "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 2.0}}
+    return {"architecture": "Pefivik", "width": width, "vocab": 32000, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "logit_softcap": 30.0,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 7919}},
+            "layers": [dict(lat, mlp=dense), dict(hg, mlp=moe), dict(lat, mlp=moe), dict(hg, mlp=dense)]}
+
+
+def pefivik_params(cfg):
+    """(matmul parameters a token multiplies with, function B -> parameters a decode step of B slots reads)"""
+    W = cfg["width"]
+    fixed, per_expert, experts, top = cfg["vocab"] * W, 0, 1, 0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        if layer["type"] == "latent_attention":
+            fixed += m["heads"] * m["dim"] * W + m["kv_rank"] * W + m["heads"] * W + m["heads"] * (m["dim"] + m["vdim"]) * m["kv_rank"] + W * m["heads"] * m["vdim"]
+        else:
+            fixed += 2 * m["heads"] * m["dim"] * W + 2 * m["heads"] * m["vdim"] * W
+        mlp = layer["mlp"]
+        if mlp["kind"] == "dense":
+            fixed += 2 * mlp["ff"] * W
+        else:
+            r = mlp["router"]
+            experts, top = r["experts"], r["top"]
+            fixed += r["experts"] * W + 3 * mlp["shared"]["ff"] * W
+            per_expert += 3 * mlp["expert"]["ff"] * W
+    return fixed + top * per_expert, lambda B: fixed + per_expert * experts * (1.0 - (1.0 - top / experts) ** B)
+
+
+def run_pefivik(args):
+    """Pefivik beside Katadra, the package's other layer-list decoder, at equal width and depth."""
+    from oracle import katadra_oracle as KO
+    from oracle import pefivik_oracle as PO
+    from llava.model import KatadraConfig, KatadraForCausalLM, PefivikConfig, PefivikForCausalLM
+    from llava._b2 import launch_count
+
+    dev = torch.device("cuda:0")
+    hbm, tfl, src = peaks()
+    pk = {"hbm_gbs": hbm, "bf16_tflops": tfl, "source": src}
+    S, N, layers = args.ctx, 64, 4
+    flush = torch.zeros(160 * 1024 * 1024 // 4, device=dev)  # 160 MB > 126 MB of L2
+    out = {"metric": "Pefivik vs Katadra (layer-list decoders) at equal width and depth", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+           "peaks": pk, "prompt": S, "decode_steps": N, "l2": "160 MB written before every timed run", "sizes": []}
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches0 = launch_count()
+    for width in [int(w) for w in args.widths.split(",")]:
+        row = {"width": width, "layers": layers}
+        cfg = pefivik_config(width)
+        w = PO.random_weights(cfg, seed=0)
+        params, params_read = pefivik_params(cfg)
+        model = PefivikForCausalLM(PefivikConfig(**cfg), {k: torch.from_numpy(np.asarray(v, np.float32)).bfloat16() for k, v in w.items()}, device=dev, dtype=torch.bfloat16,
+                                   max_batch=8, max_seq=S + N + 8, max_rows=S)
+        row["pefivik_params_total"] = int(sum(v.size for k, v in w.items() if v.ndim == 2 and k not in ("embed", "bigram", "loop.step")))
+        del w
+        row["pefivik"] = measure_layer_list(model, args, S, N, flush, pk, params, params_read)
+        del model
+        cfg = katadra_config(width, layers, S + N + 8)
+        w = KO.random_weights(cfg, seed=0)
+        kparams = sum(v.numel() for k, v in w.items() if v.dim() == 2 and k != "embed")
+        model = KatadraForCausalLM(KatadraConfig(**cfg), {k: v.bfloat16() for k, v in w.items()}, device=dev, dtype=torch.bfloat16,
+                                   max_batch=8, max_seq=S + N + 8, max_rows=S)
+        del w
+        row["katadra"] = measure_layer_list(model, args, S, N, flush, pk, kparams, lambda B: kparams)
+        del model
+        out["sizes"].append(row)
+    out["clocks"] = sampler.stop()
+    out["gpu_launches"] = launch_count() - launches0
+    print(json.dumps(out))
+
+
 def run_katadra(args):
     from oracle import katadra_oracle as KO
     from llava.model import KatadraConfig, KatadraForCausalLM
@@ -795,28 +901,8 @@ def run_katadra(args):
         model = KatadraForCausalLM(KatadraConfig(**cfg), {k: v.bfloat16() for k, v in w.items()}, device=dev, dtype=torch.bfloat16,
                                    max_batch=8, max_seq=S + N + 8, max_rows=S)
         del w
-        eng = model._ensure_engine()
-        kv = eng.new_kv(8, S + N + 8)
-        toks = torch.randint(0, 32000, (S,)).tolist()
-        t_pre = timed(lambda: eng.append_tokens(kv, 0, toks, [S - 1], restart=True), args.steps, args.warmup, flush)
-        res = {"params_matmul": params, "prefill_ms": round(t_pre, 3), "prefill_tok_s": round(S / t_pre * 1e3, 1),
-               "prefill_frac_bf16_peak": round(2.0 * params * S / (t_pre * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
-               "state_bytes_per_slot": eng.kv_bytes(1, S)}
-        for B in (1, 8):
-            for b in range(B):
-                eng.append_tokens(kv, b, toks, [], restart=True)
-            first = torch.zeros(B, dtype=torch.int32, device=dev)
-            eng.decode_greedy(kv, first, 4)                                   # eager step + graph capture
-            for b in range(B):
-                eng.append_tokens(kv, b, toks, [], restart=True)
-            t = timed(lambda: eng.decode_greedy(kv, first, N), 1, 0, flush) / N
-            moved = 2.0 * params + B * eng.kv_bytes(1, S)                      # weights once + every slot's state and key/value rows
-            res[f"decode_b{B}_ms_per_step"] = round(t, 4)
-            res[f"decode_b{B}_tok_s"] = round(B / t * 1e3, 1)
-            res[f"decode_b{B}_frac_hbm_peak"] = round(moved / (t * 1e-3) / (pk["hbm_gbs"] * 1e9), 4)
-        row["katadra"] = res
-        model.invalidate_engine()
-        del model, eng, kv
+        row["katadra"] = measure_layer_list(model, args, S, N, flush, pk, params, lambda B: params)
+        del model
         # ---- LLaMA decoder of the same width and depth ------------------------------------------------------------------------
         m = {"name": f"llama-w{width}", "hidden": width, "inter": (int(width * 8 / 3) + 255) // 256 * 256, "layers": layers, "heads": width // 128}
         lm = build_model(m, dev, 8, S + N + 8)
@@ -850,10 +936,10 @@ def run_katadra(args):
 
 def main():
     args = parse_args()
-    if args.arch == "katadra":
+    if args.arch in ("katadra", "pefivik"):
         if not torch.cuda.is_available():
-            raise RuntimeError("bench.py --arch katadra needs a B200")
-        return run_katadra(args)
+            raise RuntimeError(f"bench.py --arch {args.arch} needs a B200")
+        return run_katadra(args) if args.arch == "katadra" else run_pefivik(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -248,7 +248,7 @@ typedef struct b2_seq_model_desc {
     float logit_softcap;     /* logits <- cap * tanh(logits / cap); 0 = none */
     int32_t bigram_buckets, bigram_mul_prev, bigram_mul_cur;  /* hashed bigram embedding: row (prev * mul_prev + cur * mul_cur) mod
                                                                  buckets, row `buckets` for a sequence's first token; 0 buckets = none */
-    int32_t loop_start, loop_stop, loop_times;                /* layers [start, stop) run `times` times in a row; times <= 1: no loop */
+    int32_t loop_start, loop_stop, loop_times;                /* layers [start, stop) run `times` times in a row; times 0: no loop */
 } b2_seq_model_desc;
 int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* layers, b2_model** out);
 /* Layer RUNS of one forward pass (a looped layer counts every time): rows of b2_append_tokens' resid_out; -1 for other models */

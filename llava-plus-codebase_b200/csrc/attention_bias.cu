@@ -181,8 +181,11 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
         lo = sp * per;
         hi = min(maxpos + 1, lo + per);
     }
-    const float* K = a.kcache + ((size_t)slot * a.G + g) * a.Smax * dk;
-    const float* V = a.vcache + ((size_t)slot * a.G + g) * a.Smax * dv;
+    // cache slabs [slot][head][position][size], or (kv_row_stride > 0) one matrix [position][head * size] made for this call
+    const bool mat = a.kv_row_stride > 0;
+    const size_t krs = mat ? (size_t)a.kv_row_stride : (size_t)dk, vrs = mat ? (size_t)a.kv_row_stride_v : (size_t)dv;
+    const float* K = mat ? a.kcache + (size_t)g * dk : a.kcache + ((size_t)slot * a.G + g) * a.Smax * dk;
+    const float* V = mat ? a.vcache + (size_t)g * dv : a.vcache + ((size_t)slot * a.G + g) * a.Smax * dv;
     float m[TL_PPW], l[TL_PPW], o[TL_PPW][MAXC];
     int ppos[TL_PPW];
 #pragma unroll
@@ -200,13 +203,13 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
             const int dk4 = dk >> 2;
             for (int e = tid; e < nk * dk4; e += TL_WARPS * 32) {
                 const int kk = e / dk4, d4 = e % dk4;
-                *reinterpret_cast<float4*>(sK + kk * dkp + d4 * 4) = *reinterpret_cast<const float4*>(K + (size_t)(j0 + kk) * dk + d4 * 4);
+                *reinterpret_cast<float4*>(sK + kk * dkp + d4 * 4) = *reinterpret_cast<const float4*>(K + (size_t)(j0 + kk) * krs + d4 * 4);
             }
         } else {
-            for (int e = tid; e < nk * dk; e += TL_WARPS * 32) sK[(e / dk) * dkp + e % dk] = K[(size_t)j0 * dk + e];
+            for (int e = tid; e < nk * dk; e += TL_WARPS * 32) sK[(e / dk) * dkp + e % dk] = K[(size_t)(j0 + e / dk) * krs + e % dk];
         }
         if (!shared_kv)
-            for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)j0 * dv + e];
+            for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)(j0 + e / dv) * vrs + e % dv];
         __syncthreads();
         // The warp's pairs go through the tile TOGETHER: a lane reads its key row once for all of them, and a value element
         // once per key for all of them (shared-memory bandwidth, not the FMA pipe, limits this loop).
@@ -307,46 +310,43 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
     }
 }
 
-// one warp per (row, head): combines the key splits in split order; lane s first turns split s's (max, sum) into its weight
-template <int MAXC>
-__global__ void attn_merge_kernel(BiasAttnArgs a) {
-    const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (w >= a.rows * a.H) return;
+// one block per (row, head): every thread turns the splits' (max, sum) into weights (nsplit <= 64 values from L1) and combines
+// its value columns in split order
+__global__ void __launch_bounds__(128) attn_merge_kernel(BiasAttnArgs a) {
+    const int w = blockIdx.x;
     const int r = w / a.H, h = w % a.H;
     if (a.row_pos[r] < 0) return;
-    const float* part = a.partial + (size_t)w * a.nsplit * (a.dv + 2);
-    float mx = -INFINITY;
-    for (int s = lane; s < a.nsplit; s += 32) mx = fmaxf(mx, part[(size_t)s * (a.dv + 2)]);
-    mx = warp_max(mx);
-    const float sk = a.sink != nullptr ? a.sink[h] : -INFINITY;
-    mx = fmaxf(mx, sk);
-    float wgt[2] = {0.f, 0.f}, lsum = (a.sink != nullptr && lane == 0) ? expf(sk - mx) : 0.f;   // nsplit <= 64: splits lane and lane + 32
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int s = lane + 32 * i;
-        if (s < a.nsplit) {
-            const float* ps = part + (size_t)s * (a.dv + 2);
-            if (ps[1] > 0.f) { wgt[i] = expf(ps[0] - mx); lsum = fmaf(ps[1], wgt[i], lsum); }
+    const int stride = a.dv + 2;
+    const float* part = a.partial + (size_t)w * a.nsplit * stride;
+    __shared__ float wgt[64];
+    __shared__ float inv_s;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float mx = -INFINITY;
+        for (int s = lane; s < a.nsplit; s += 32)
+            if (part[(size_t)s * stride + 1] > 0.f) mx = fmaxf(mx, part[(size_t)s * stride]);
+        mx = warp_max(mx);
+        const float sk = a.sink != nullptr ? a.sink[h] : -INFINITY;
+        mx = fmaxf(mx, sk);
+        float lsum = (a.sink != nullptr && lane == 0) ? expf(sk - mx) : 0.f;
+        for (int s = lane; s < a.nsplit; s += 32) {
+            const float* ps = part + (size_t)s * stride;
+            const float ws = ps[1] > 0.f ? expf(ps[0] - mx) : 0.f;
+            wgt[s] = ws;
+            lsum = fmaf(ps[1], ws, lsum);
         }
+        lsum = warp_sum(lsum);
+        if (lane == 0) inv_s = 1.f / lsum;
     }
-    const float inv = 1.f / warp_sum(lsum);
-    float acc[MAXC];
-#pragma unroll
-    for (int c = 0; c < MAXC; ++c) acc[c] = 0.f;
-    for (int s = 0; s < a.nsplit; ++s) {
-        const float ws = __shfl_sync(0xffffffffu, s < 32 ? wgt[0] : wgt[1], s & 31);
-        if (ws == 0.f) continue;
-        const float* ps = part + (size_t)s * (a.dv + 2) + 2;
-#pragma unroll
-        for (int c = 0; c < MAXC; ++c) {
-            const int d = lane + 32 * c;
-            if (d < a.dv) acc[c] = fmaf(ps[d], ws, acc[c]);
+    __syncthreads();
+    const float inv = inv_s;
+    for (int d = threadIdx.x; d < a.dv; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < a.nsplit; ++s) {
+            const float ws = wgt[s];
+            if (ws != 0.f) acc = fmaf(part[(size_t)s * stride + 2 + d], ws, acc);
         }
-    }
-#pragma unroll
-    for (int c = 0; c < MAXC; ++c) {
-        const int d = lane + 32 * c;
-        if (d < a.dv) a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = acc[c] * inv;
+        a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = acc * inv;
     }
 }
 
@@ -355,6 +355,7 @@ int check_args(const BiasAttnArgs& a, const char* who) {
     B2_CHECK_ARG(a.H > 0 && a.G > 0 && a.H % a.G == 0, "%s: %d query heads cannot share %d key/value heads", who, a.H, a.G);
     B2_CHECK_ARG(a.dk > 0 && a.dk <= 512 && a.dv > 0 && a.dv <= 512, "%s: head sizes %d / %d exceed 512", who, a.dk, a.dv);
     B2_CHECK_ARG(a.vcache != a.kcache || a.dk == a.dv, "%s: keys that are also the values need dk == dv", who);
+    B2_CHECK_ARG(a.kv_row_stride == 0 || (a.kv_row_stride_v > 0 && a.tile_rows >= 1 && a.vcache != a.kcache), "%s: key/value matrices need both pitches and the tiled kernel", who);
     return 0;
 }
 }  // namespace
@@ -374,7 +375,7 @@ int launch_tile(const BiasAttnArgs& a, int QT, int HC, dim3 grid, size_t smem, c
     attn_tile_kernel<VEC, MAXC><<<grid, TL_WARPS * 32, smem, st>>>(a, QT, HC);
     B2_LAUNCH_CHECK();
     if (a.nsplit > 1) {
-        attn_merge_kernel<MAXC><<<(a.rows * a.H + 7) / 8, 256, 0, st>>>(a);
+        attn_merge_kernel<<<a.rows * a.H, 128, 0, st>>>(a);
         B2_LAUNCH_CHECK();
     }
     return 0;
@@ -407,7 +408,7 @@ int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t st) {
     else attn_bias_kernel<false><<<grid, AT_WARPS * 32, smem, st>>>(a);
     B2_LAUNCH_CHECK();
     if (a.nsplit > 1) {
-        attn_merge_kernel<AT_MAXC><<<(warps + 7) / 8, 256, 0, st>>>(a);
+        attn_merge_kernel<<<warps, 128, 0, st>>>(a);
         B2_LAUNCH_CHECK();
     }
     return 0;

@@ -300,6 +300,10 @@ struct GroupedLinearArgs {
     int round_a = 0;
 };
 int linear_grouped_f32(const GroupedLinearArgs& g, cudaStream_t stream);
+// `batch` small Linears in one launch on a handful of rows (a decode step's per-head products): for b < batch,
+// out[m, b * o_bs + n] = sum_k A[m, b * a_bs + k] * W[b * w_bs + n * K + k], m < M <= 8; weights in w_dtype, fp32 accumulation
+int linear_batched_rows_f32(const float* A, int64_t lda, int64_t a_bs, const void* W, int64_t w_bs, int w_dtype, float* out, int64_t ld_out,
+                            int64_t o_bs, int batch, int M, int N, int K, int round_a, cudaStream_t stream);
 enum { GROUPED_TILE_ROWS = 64 };
 
 // ---- mixture of experts (moe.cu) ------------------------------------------------------------------------------------------
@@ -412,6 +416,8 @@ struct BiasAttnArgs {
     float eps = 0.f, scale = 1.f, softcap = 0.f;  // softcap <= 0: none
     float temp_coef = 0.f, temp_every = 1.f;      // q *= 1 + coef * ln(floor((p + 1) / every) + 1)
     const int32_t* row_slot = nullptr; const int32_t* row_pos = nullptr;
+    int64_t kv_row_stride = 0, kv_row_stride_v = 0;  // > 0: kcache / vcache are matrices [position][G * dk] / [position][G * dv] of the call's
+                                                  // one slot (keys and values made for this call) with these pitches, not cache slabs
     const float* sink = nullptr;                  // [H] or null: exp(sink[h]) joins the softmax denominator (no key, no value)
     float* partial = nullptr; int nsplit = 1;     // split-KV scratch [rows*H*nsplit*(dv+2)] when nsplit > 1
     int tile_rows = 0;                            // consecutive rows that share a slot (a prompt portion: its rows; a decode step: 1);

@@ -339,6 +339,64 @@ __global__ void __launch_bounds__(256) linear_grouped_rows_kernel(GroupedLinearA
     if (lane == 0) lin_store(g.out + (size_t)m * g.ld_out + n, acc, nullptr, n, g.act, 1.f, 0);
 }
 
+// batched small Linears of a decode step: block = 8 output columns of one batch entry (a head), one warp per column; the
+// weight row is read once and multiplied with every row of the step
+template <typename TW, bool VEC>
+__global__ void __launch_bounds__(256) linear_batched_rows_kernel(const float* __restrict__ A, int64_t lda, int64_t a_bs, const TW* __restrict__ W,
+                                                                  int64_t w_bs, float* __restrict__ out, int64_t ld_out, int64_t o_bs, int M, int N,
+                                                                  int K, int round_a) {
+    const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    const TW* w = W + (size_t)b * w_bs + (size_t)n * K;
+    const float* a = A + (size_t)b * a_bs;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; ++m) acc[m] = 0.f;
+    if (VEC) {
+        for (int k0 = lane * 8; k0 < K; k0 += 256) {
+            float wv[8];
+            ld_w8(w + k0, wv);
+#pragma unroll
+            for (int m = 0; m < MR; ++m) {
+                if (m < M) {
+                    float av[8];
+                    ld_w8(a + (size_t)m * lda + k0, av);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[m] = fmaf(round_a ? round_bf16(av[e]) : av[e], wv[e], acc[m]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = ld_w(w + k);
+#pragma unroll
+            for (int m = 0; m < MR; ++m)
+                if (m < M) { const float av = a[(size_t)m * lda + k]; acc[m] = fmaf(round_a ? round_bf16(av) : av, wv, acc[m]); }
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; ++m) {
+        float v = acc[m];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && m < M) out[(size_t)m * ld_out + (size_t)b * o_bs + n] = v;
+    }
+}
+
+template <typename TW>
+int launch_batched_rows(const float* A, int64_t lda, int64_t a_bs, const void* W, int64_t w_bs, float* out, int64_t ld_out, int64_t o_bs, int batch, int M,
+                        int N, int K, int round_a, cudaStream_t st) {
+    const bool vec = K % 8 == 0 && lda % 4 == 0 && a_bs % 4 == 0 && w_bs % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(W) & 15) == 0;
+    dim3 grid((N + 7) / 8, batch);
+    const TW* w = reinterpret_cast<const TW*>(W);
+    if (vec) linear_batched_rows_kernel<TW, true><<<grid, 256, 0, st>>>(A, lda, a_bs, w, w_bs, out, ld_out, o_bs, M, N, K, round_a);
+    else linear_batched_rows_kernel<TW, false><<<grid, 256, 0, st>>>(A, lda, a_bs, w, w_bs, out, ld_out, o_bs, M, N, K, round_a);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
 template <typename TW>
 int launch_grouped(const GroupedLinearArgs& g, cudaStream_t st) {
     if (g.tile_rows == 1) {
@@ -355,6 +413,14 @@ int launch_grouped(const GroupedLinearArgs& g, cudaStream_t st) {
     return 0;
 }
 }  // namespace
+
+int linear_batched_rows_f32(const float* A, int64_t lda, int64_t a_bs, const void* W, int64_t w_bs, int w_dtype, float* out, int64_t ld_out,
+                            int64_t o_bs, int batch, int M, int N, int K, int round_a, cudaStream_t st) {
+    B2_CHECK_ARG(A && W && out && batch > 0 && M > 0 && M <= MR && N > 0 && K > 0, "linear_batched_rows: bad argument (batch=%d M=%d N=%d K=%d)", batch, M, N, K);
+    B2_CHECK_ARG(w_dtype == DT_F32 || w_dtype == DT_BF16, "linear_batched_rows: weights must be fp32 or bf16");
+    return w_dtype == DT_F32 ? launch_batched_rows<float>(A, lda, a_bs, W, w_bs, out, ld_out, o_bs, batch, M, N, K, round_a, st)
+                             : launch_batched_rows<__nv_bfloat16>(A, lda, a_bs, W, w_bs, out, ld_out, o_bs, batch, M, N, K, round_a, st);
+}
 
 int linear_grouped_f32(const GroupedLinearArgs& g, cudaStream_t st) {
     B2_CHECK_ARG(g.A && g.W && g.out && g.tile_group && g.M > 0 && g.N > 0 && g.K > 0, "linear_grouped: bad argument (M=%d N=%d K=%d)", g.M, g.N, g.K);

@@ -21,7 +21,7 @@ struct SeqWeights {   // tensors of one layer that owns its weights
     DevBuf mu, r_w, k_w, v_w, g_w, w1, w2, w0, bonus, rnorm, ro_w;                       // RWKV
     DevBuf up_w, down_w;                                                                 // feed-forward
     // pre-norm designs
-    DevBuf qdg_w, dkv_norm, ukT, uv_w, sink;            // latent attention: [q | dkv | g] fused; W_uk per head transposed to [rank][dim]
+    DevBuf qdg_w, dkv_norm, uk_w, ukT, uv_w, sink;      // latent attention: [q | dkv | g] fused; W_uk as stored and per head transposed to [rank][dim]
     DevBuf qfv_w, f_b, lower, hnorm;                    // HGRN2: [q | f | v] fused
     DevBuf up_b, down_b, down_b16, act_coef;            // PolyNorm feed-forward (bias of the second product also as bf16: GEMM epilogue)
     DevBuf router_w, egu_w, ed_w, sgu_w, sd_w;          // experts: [E][gate | up][width], [E][width][ff]; shared expert [gate | up], down
@@ -74,6 +74,8 @@ struct SeqLayerState {
 struct SeqState {
     std::vector<SeqLayerState> layer;  // one per layer RUN
     DevBuf last_tok;                   // int32 [slots]: the token in front of the next one (hashed bigram embedding)
+    DevBuf kmat, vmat;                 // latent attention, long prompt portions: per-head keys / values of one slot's positions [Smax][heads*size]
+    int kmat_ld = 0, vmat_ld = 0;
     DevBuf attn_partial;
     int nsplit_max = 1;
 };
@@ -172,6 +174,14 @@ struct Lin {  // one Linear call on the model's compute dtype
     }
 };
 
+int router_rows(int experts) { return std::max(32, (experts + 7) / 8 * 8); }   // rows of the (zero-padded) router matrix
+
+int latent_materialise_rows() {  // prompt portions of at least this many rows make per-head keys / values instead of absorbing W_uk / W_uv
+    const char* e = getenv("B2_LATENT_MATERIALISE_ROWS");
+    const int v = e != nullptr ? atoi(e) : 0;
+    return v >= 1 ? v : 64;
+}
+
 int attn_nsplit(int rows, int G, int max_seq) {
     // a decode step has few (row, key/value head) CTAs: cut the keys so that the step fills the SMs twice over, but keep
     // at least 64 keys per cut at the cache's capacity
@@ -188,7 +198,8 @@ int attn_nsplit(int rows, int G, int max_seq) {
 // ------------------------------------------------------------------------------------------------------------------
 // forward over R rows described by the model's row map (nseg segments). x holds the embedded rows on entry.
 // ------------------------------------------------------------------------------------------------------------------
-static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out, cudaStream_t st) {
+// slot / ctx_end: for a prompt portion (nseg == 1) its slot and the slot's length after the call; 0 / 0 for a decode step
+static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ctx_end, float* resid_out, cudaStream_t st) {
     SeqModel& s = *m->seq;
     SeqState& state = *kv->seq;
     const int width = s.d.width;
@@ -220,27 +231,55 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
                 B2_TRY(lin(xn, width, W.qdg_w, L.pproj, width, proj, L.pproj_ld, R));
                 B2_TRY(latent_append_f32(proj + L.pq, L.pproj_ld, W.dkv_norm.as<float>(), S.lat.as<float>(), s.row_slot.as<int32_t>(),
                                          s.row_pos.as<int32_t>(), R, rank, kv->max_seq, eps, st));
-                // absorbed form: q_h -> W_uk_h^T q_h lives in the latent space, so scores and values read the cached rows directly
-                float* qabs = s.qabs.as<float>();
-                const int64_t lq = (int64_t)H * rank;
-                for (int h = 0; h < H; ++h)
-                    B2_TRY(lin(proj + (size_t)h * dk, L.pproj_ld, W.ukT, rank, dk, qabs + (size_t)h * rank, lq, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * rank));
                 BiasAttnArgs aa;
-                aa.q = qabs; aa.ldq = lq;
-                aa.kcache = S.lat.as<float>(); aa.vcache = S.lat.as<float>();
-                aa.out = s.olat.as<float>(); aa.ldo = lq;
                 aa.sink = W.sink.as<float>();
-                aa.H = H; aa.G = 1; aa.dk = rank; aa.dv = rank; aa.Smax = kv->max_seq; aa.rows = R;
+                aa.H = H; aa.Smax = kv->max_seq; aa.rows = R;
                 aa.eps = eps; aa.scale = d.la_scale; aa.softcap = 0.f;
                 aa.row_slot = s.row_slot.as<int32_t>(); aa.row_pos = s.row_pos.as<int32_t>();
-                aa.nsplit = attn_nsplit(R, (H + 31) / 32, kv->max_seq);
                 aa.tile_rows = max_n;
-                if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
                 aa.partial = state.attn_partial.as<float>();
-                B2_TRY(attn_bias_f32(aa, st));
                 float* y = s.y.as<float>();
-                for (int h = 0; h < H; ++h)
-                    B2_TRY(lin(s.olat.as<float>() + (size_t)h * rank, lq, W.uv_w, dv, rank, y + (size_t)h * dv, L.pv, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * dv));
+                if (nseg == 1 && R >= latent_materialise_rows() && ctx_end > 0) {
+                    // a long portion: per-head keys and values of every position of the slot so far are made from the cached
+                    // rows with two products, and the attention runs over them with the heads' own sizes
+                    const float* lat = S.lat.as<float>() + (size_t)slot * kv->max_seq * rank;
+                    for (int m0 = 0; m0 < ctx_end; m0 += s.rows) {
+                        const int mc = std::min(s.rows, ctx_end - m0);
+                        B2_TRY(lin(lat + (size_t)m0 * rank, rank, W.uk_w, L.pq, rank, state.kmat.as<float>() + (size_t)m0 * state.kmat_ld, state.kmat_ld, mc));
+                        B2_TRY(lin(lat + (size_t)m0 * rank, rank, W.uv_w, L.pv, rank, state.vmat.as<float>() + (size_t)m0 * state.vmat_ld, state.vmat_ld, mc));
+                    }
+                    aa.q = proj; aa.ldq = L.pproj_ld;
+                    aa.kcache = state.kmat.as<float>(); aa.vcache = state.vmat.as<float>();
+                    aa.kv_row_stride = state.kmat_ld; aa.kv_row_stride_v = state.vmat_ld;
+                    aa.out = y; aa.ldo = L.pv;
+                    aa.G = H; aa.dk = dk; aa.dv = dv; aa.nsplit = 1;
+                    B2_TRY(attn_bias_f32(aa, st));
+                } else {
+                    // absorbed form: q_h -> W_uk_h^T q_h lives in the latent space, so scores and values read the cached rows
+                    // directly, and W_uv_h carries the latent-space output to the head's values
+                    float* qabs = s.qabs.as<float>();
+                    const int64_t lq = (int64_t)H * rank;
+                    const int round_a = s.d.compute == B2_COMPUTE_BF16;
+                    if (R <= 8) {
+                        B2_TRY(linear_batched_rows_f32(proj, L.pproj_ld, dk, W.ukT.p, (int64_t)rank * dk, s.w_dtype, qabs, lq, rank, H, R, rank, dk, round_a, st));
+                    } else {
+                        for (int h = 0; h < H; ++h)
+                            B2_TRY(lin(proj + (size_t)h * dk, L.pproj_ld, W.ukT, rank, dk, qabs + (size_t)h * rank, lq, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * rank));
+                    }
+                    aa.q = qabs; aa.ldq = lq;
+                    aa.kcache = S.lat.as<float>(); aa.vcache = S.lat.as<float>();
+                    aa.out = s.olat.as<float>(); aa.ldo = lq;
+                    aa.G = 1; aa.dk = rank; aa.dv = rank;
+                    aa.nsplit = attn_nsplit(R, (H + 31) / 32, kv->max_seq);
+                    if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
+                    B2_TRY(attn_bias_f32(aa, st));
+                    if (R <= 8) {
+                        B2_TRY(linear_batched_rows_f32(s.olat.as<float>(), lq, rank, W.uv_w.p, (int64_t)dv * rank, s.w_dtype, y, L.pv, dv, H, R, dv, rank, round_a, st));
+                    } else {
+                        for (int h = 0; h < H; ++h)
+                            B2_TRY(lin(s.olat.as<float>() + (size_t)h * rank, lq, W.uv_w, dv, rank, y + (size_t)h * dv, L.pv, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * dv));
+                    }
+                }
                 B2_TRY(head_gate_f32(y, L.pv, proj + L.pq + rank, L.pproj_ld, s.gated.as<float>(), L.pv, R, H, dv, st));
                 B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, x, width, R, LIN_NONE, rm, 1));
             } else {
@@ -270,9 +309,9 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, float* resid_out
                     B2_TRY(lin(s.ffa.as<float>(), d.ff, W.down_w, width, d.ff, x, width, R, LIN_NONE, rm, 1, W.down_b.as<float>(), 0, W.down_b16.p));
                 } else if (d.ff_kind == B2_FF_MOE) {
                     const int E = d.moe_experts, top = d.moe_top, ff = d.ff;
-                    B2_TRY(lin(xn, width, W.router_w, E, width, s.rlogit.as<float>(), (E + 7) / 8 * 8, R));
+                    B2_TRY(lin(xn, width, W.router_w, router_rows(E), width, s.rlogit.as<float>(), router_rows(E), R));
                     MoeRouteArgs ra;
-                    ra.logits = s.rlogit.as<float>(); ra.ld = (E + 7) / 8 * 8; ra.rows = R; ra.experts = E; ra.top = top;
+                    ra.logits = s.rlogit.as<float>(); ra.ld = router_rows(E); ra.rows = R; ra.experts = E; ra.top = top;
                     ra.groups = d.moe_groups; ra.keep = d.moe_keep; ra.scale = d.moe_scale;
                     ra.idx = s.moe_idx.as<int32_t>(); ra.w = s.moe_w.as<float>();
                     B2_TRY(moe_route_f32(ra, st));
@@ -433,7 +472,7 @@ int seq_decode_launch(b2_model* m, b2_kv* kv, int B, int slot0, cudaStream_t st)
     RowMap rm{s.segs.as<SeqSeg>(), s.row_slot.as<int32_t>(), s.row_pos.as<int32_t>()};
     B2_TRY(rowmap_decode(rm, kv->len_dev.as<int32_t>(), kv->sstate.as<SampleState>(), kv->rows_dev.as<RowState>(), slot0, B, st));
     B2_TRY(seq_embed(m, kv, kv->tok.as<int32_t>() + slot0, B, B, st));
-    B2_TRY(seq_forward(m, kv, B, B, nullptr, st));
+    B2_TRY(seq_forward(m, kv, B, B, 0, 0, nullptr, st));
     B2_TRY(seq_head(m, nullptr, B, m->logits.as<float>(), s.d.vocab, st));
     B2_TRY(sample_publish(m->logits.as<float>(), s.d.vocab, B, kv->sstate.as<SampleState>(), kv->rows_dev.as<RowState>() + slot0,
                           kv->tok.as<int32_t>() + slot0, kv->out_tokens.as<int32_t>(), kv->step_counter.as<int32_t>(),
@@ -457,7 +496,7 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
         B2_TRY(want_shape(key, shape, ndim, rows, width)); s.got[k] = 1;
         return put_tensor(s.bigram, WD, (size_t)rows * width, 0, ptr, dt, rows * width);
     }
-    if (k == "loop.step" && s.d.loop_times > 1) {
+    if (k == "loop.step" && s.d.loop_times >= 1) {
         B2_TRY(want_shape(key, shape, ndim, s.d.loop_times, width)); s.got[k] = 1;
         return put_tensor(s.loop_step, DT_F32, (size_t)s.d.loop_times * width, 0, ptr, dt, (int64_t)s.d.loop_times * width);
     }
@@ -495,16 +534,13 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
             if (r == "mix.uv") return mat(W.uv_w, (int64_t)H * dv, rank);
             if (r == "mix.o") return mat(W.o_w, width, (int64_t)H * dv);
             if (r == "mix.uk") {
-                // stored per head as [rank][dim]: the query is carried into the latent space by a Linear with this matrix
-                B2_TRY(want_shape(key, shape, ndim, (int64_t)H * dk, rank));
-                DevBuf tmp;
-                B2_TRY(put_tensor(tmp, WD, (size_t)H * dk * rank, 0, ptr, dt, (int64_t)H * dk * rank));
+                // kept as stored (keys of long prompt portions) and per head as [rank][dim] (the query is carried into the latent
+                // space by a Linear with this matrix)
+                B2_TRY(mat(W.uk_w, (int64_t)H * dk, rank));
                 int rc = W.ukT.alloc(((size_t)H * rank + 8) * dk * esz(WD));
                 if (rc == 0) rc = cudaMemset(W.ukT.p, 0, W.ukT.bytes) == cudaSuccess ? 0 : -2;
-                if (rc == 0) rc = transpose_blocks(tmp.p, W.ukT.p, H, dk, rank, (int)esz(WD), 0);
+                if (rc == 0) rc = transpose_blocks(W.uk_w.p, W.ukT.p, H, dk, rank, (int)esz(WD), 0);
                 cudaStreamSynchronize(0);
-                tmp.free();
-                W.got[r] = 1;
                 return rc;
             }
         } else if (d.type == B2_MIXER_HGRN2) {
@@ -528,7 +564,11 @@ int seq_set_weight(b2_model* m, const char* key, const void* ptr, const int64_t*
             }
         } else if (d.ff > 0 && d.ff_kind == B2_FF_MOE) {
             const int E = d.moe_experts, ff = d.ff, sf = d.moe_shared_ff;
-            if (r == "mlp.router") return mat(W.router_w, E, width);
+            if (r == "mlp.router") {   // at least 32 rows (zeros behind the experts): the tensor-core product of a prompt portion takes it
+                B2_TRY(want_shape(key, shape, ndim, E, width));
+                W.got[r] = 1;
+                return put_tensor(W.router_w, WD, (size_t)router_rows(E) * width, 0, ptr, dt, (int64_t)E * width);
+            }
             if (sf > 0) {
                 if (r == "mlp.shared.gate") return part(W.sgu_w, 2 * sf, 0, sf, width);
                 if (r == "mlp.shared.up") return part(W.sgu_w, 2 * sf, sf, sf, width);
@@ -647,7 +687,7 @@ int seq_finalize(b2_model* m) {
     std::vector<std::string> top = {"embed", "head", "final.norm"};
     if (!pre) top.push_back("final.norm.b");
     if (s.d.bigram_buckets > 0) top.push_back("bigram");
-    if (s.d.loop_times > 1) top.push_back("loop.step");
+    if (s.d.loop_times >= 1) top.push_back("loop.step");
     for (const std::string& n : top)
         if (!s.got.count(n) && missing.size() < 600) { missing += n; missing += ' '; }
     for (size_t i = 0; i < s.layers.size(); ++i) {
@@ -677,7 +717,7 @@ int seq_finalize(b2_model* m) {
             moe_top = std::max(moe_top, L.d.moe_top); moe_e = std::max(moe_e, L.d.moe_experts); moe_ff = std::max(moe_ff, L.d.ff);
         }
     }
-    pw = std::max(pw, (moe_e + 7) / 8 * 8);
+
     s.proj_w = pw; s.act_w = aw; s.y_w = yw; s.rp_w = rw; s.rank_w = kw; s.ff_w = fw;
     const size_t R = (size_t)s.rows;
     B2_TRY(s.x.alloc(R * width * F4));
@@ -705,7 +745,7 @@ int seq_finalize(b2_model* m) {
         s.moe_tiles = (int)((R * moe_top + (size_t)moe_e * (GROUPED_TILE_ROWS - 1) + GROUPED_TILE_ROWS - 1) / GROUPED_TILE_ROWS);
         s.moe_rows = s.moe_tiles * GROUPED_TILE_ROWS;
         const size_t P = (size_t)s.moe_rows;
-        B2_TRY(s.rlogit.alloc(R * ((moe_e + 7) / 8 * 8) * F4));
+        B2_TRY(s.rlogit.alloc(R * router_rows(moe_e) * F4));
         B2_TRY(s.moe_idx.alloc(R * moe_top * 4));
         B2_TRY(s.moe_w.alloc(R * moe_top * F4));
         B2_TRY(s.moe_pos.alloc(R * moe_top * 4));
@@ -737,7 +777,7 @@ void seq_model_free(b2_model* m) {
     for (SeqWeights& W : s.w) {
         DevBuf* bs[] = {&W.norm1, &W.norm1_b, &W.norm2, &W.norm2_b, &W.in_w, &W.conv_w, &W.conv_b, &W.dt_bias, &W.a_log, &W.skip, &W.mnorm, &W.o_w,
                         &W.lproj_w, &W.rel, &W.lo_w, &W.mu, &W.r_w, &W.k_w, &W.v_w, &W.g_w, &W.w1, &W.w2, &W.w0, &W.bonus, &W.rnorm, &W.ro_w,
-                        &W.up_w, &W.down_w, &W.qdg_w, &W.dkv_norm, &W.ukT, &W.uv_w, &W.sink, &W.qfv_w, &W.f_b, &W.lower, &W.hnorm, &W.up_b, &W.down_b,
+                        &W.up_w, &W.down_w, &W.qdg_w, &W.dkv_norm, &W.uk_w, &W.ukT, &W.uv_w, &W.sink, &W.qfv_w, &W.f_b, &W.lower, &W.hnorm, &W.up_b, &W.down_b,
                         &W.down_b16, &W.act_coef, &W.router_w, &W.egu_w, &W.ed_w, &W.sgu_w, &W.sd_w};
         for (DevBuf* b : bs) b->free();
     }
@@ -817,6 +857,14 @@ int seq_kv_alloc(b2_kv* kv) {
             maxdv = std::max(maxdv, d.a_vdim);
         }
     }
+    int kw = 0, vw = 0;
+    for (const SeqLayerInfo& L : s.layers)
+        if (L.d.type == B2_MIXER_LATENT_ATTN) { kw = std::max(kw, (L.pq + 7) / 8 * 8); vw = std::max(vw, (L.pv + 7) / 8 * 8); }
+    if (kw > 0) {
+        kv->seq->kmat_ld = kw; kv->seq->vmat_ld = vw;
+        B2_TRY(kv->seq->kmat.alloc(Smax * kw * F4));
+        B2_TRY(kv->seq->vmat.alloc(Smax * vw * F4));
+    }
     kv->seq->nsplit_max = 64;
     B2_TRY(kv->seq->attn_partial.alloc((size_t)8 * maxH * kv->seq->nsplit_max * (maxdv + 2) * F4));
     return 0;
@@ -829,6 +877,8 @@ void seq_kv_free(b2_kv* kv) {
         for (DevBuf* b : bs) b->free();
     }
     kv->seq->last_tok.free();
+    kv->seq->kmat.free();
+    kv->seq->vmat.free();
     kv->seq->attn_partial.free();
     delete kv->seq;
     kv->seq = nullptr;
@@ -934,7 +984,7 @@ int b2_seq_model_create(const b2_seq_model_desc* desc, const b2_seq_layer_desc* 
     }
     // layer runs: the layers in order, the looped block `times` times in a row
     {
-        const bool looped = d.loop_times > 1;
+        const bool looped = d.loop_times >= 1;   // one pass is still a pass: its vector is added in front of it
         if (looped && !(d.loop_start >= 0 && d.loop_start < d.loop_stop && d.loop_stop <= d.n_layers)) {
             set_error("b2_seq_model_create: loop [%d, %d) x %d does not fit %d layers", d.loop_start, d.loop_stop, d.loop_times, d.n_layers);
             delete s;
@@ -984,7 +1034,7 @@ int b2_append_tokens(b2_model* m, b2_kv* kv, int slot, const int32_t* tokens_hos
     // a slot that starts over begins from position 0 whatever its device-side length says
     B2_TRY(rowmap_portion(rm, kv->len_dev.as<int32_t>(), slot, n, start == 0 ? 1 : 0, st));
     B2_TRY(seq_embed(m, kv, s.tok.as<int32_t>(), n, 1, st));
-    B2_TRY(seq_forward(m, kv, n, 1, resid_out, st));
+    B2_TRY(seq_forward(m, kv, n, 1, slot, start + n, resid_out, st));
     if (n_want > 0) {
         B2_CUDA_CHECK(cudaMemcpyAsync(s.want.p, want_host, (size_t)n_want * 4, cudaMemcpyHostToDevice, st));
         cudaPointerAttributes attr;

@@ -25,7 +25,9 @@ class PefivikConfig(LayerListConfig):
         if bg:
             d.update(bigram_buckets=int(bg["buckets"]), bigram_mul_prev=int(bg["mul_prev"]), bigram_mul_cur=int(bg["mul_cur"]))
         loop = c.get("loop")
-        if loop and int(loop["times"]) > 1 and int(loop["stop"]) > int(loop["start"]):
+        if loop and int(loop["stop"]) > int(loop["start"]):
+            if int(loop["times"]) < 1:
+                raise ValueError("loop.times must be at least 1")
             d.update(loop_start=int(loop["start"]), loop_stop=int(loop["stop"]), loop_times=int(loop["times"]))
         return d
 

@@ -195,7 +195,7 @@ def bf16_round(a):
     """Round float32 values to the nearest bfloat16 (ties to even), as a checkpoint stores them."""
     u = np.asarray(a, np.float32).view(np.uint32).astype(np.uint64)
     u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
-    return u.astype(np.uint32).view(np.float32)
+    return np.asarray(u.astype(np.uint32).view(np.float32))
 
 
 def random_weights(cfg, seed=0, gain=1.0):

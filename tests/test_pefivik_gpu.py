@@ -49,9 +49,10 @@ def config(layers, width=72, vocab=150, eps=1e-5, loop=None, bigram=(61, 7, 13),
 
 
 CFG_MAIN = config([layer(LAT, DENSE), layer(HG, MOE), layer(LAT, MOE), layer(HG, None)], loop=(1, 3, 3))
-# one bucket (every bigram hashes to row 0), multiplier 1, no soft-cap, no loop, odd sizes
-CFG_ODD = config([layer(HG_ODD, DENSE_ODD), layer(LAT_ODD, MOE_ONE)], width=50, vocab=77, eps=1e-3, bigram=(1, 1, 1), mult=1.0, softcap=None)
-# the loop covers every layer; big hash multipliers; one pass declared (times 1 = no loop) is covered by CFG_ODD's absence
+# one bucket (every bigram hashes to row 0), multiplier 1, no soft-cap, a "loop" of one pass (its vector is still added), odd sizes
+CFG_ODD = config([layer(HG_ODD, DENSE_ODD), layer(LAT_ODD, MOE_ONE)], width=50, vocab=77, eps=1e-3, bigram=(1, 1, 1), mult=1.0, softcap=None,
+                 loop=(1, 2, 1))
+# the loop covers every layer; big hash multipliers
 CFG_LOOP_ALL = config([layer(LAT_ONE, MOE_SINGLES), layer(HG_BIG, DENSE)], width=64, loop=(0, 2, 2), bigram=(521, 1000003, 999983), mult=0.9)
 CFG_TAIL_LOOP = config([layer(HG, None), layer(LAT_MANY, DENSE_ODD)], width=48, loop=(1, 2, 2), mult=0.5)
 
@@ -268,6 +269,24 @@ def test_far_keys_and_tile_edges_in_prompts_portions_and_decoding():
     assert err(run_schedule(eng, kv, 0, toks, [T]), ref) < 2e-4, "whole prompt"
     assert err(run_schedule(eng, kv, 1, toks, [31, 2, 33, 64, 1, 95, 2, 2, 130]), ref) < 2e-4, "portions that end at and around tile edges, then decode steps"
     assert err(run_schedule(eng, kv, 0, toks, [300]), ref) < 2e-4, "120 decode steps over split keys"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_absorbed_and_per_head_attention_agree(dtype, monkeypatch):
+    """Long prompt portions make per-head keys and values from the cached latent rows; short ones and decode steps carry the
+    query into the latent space instead. Both forms, forced on the same prompt and portions, give the same logits."""
+    cfg = config([layer(LAT, None), layer(LAT_WIDE, DENSE), layer(LAT_MANY, None)], loop=(0, 2, 2))
+    model, w = build(cfg, dtype, max_seq=512, max_rows=160)     # fewer workspace rows than positions: the keys are made in pieces
+    eng = model._ensure_engine()
+    kv = eng.new_kv(2, 512)
+    toks = tokens_for(cfg, 300, seed=19)
+    ref, _ = O.forward(cfg, w, toks)
+    got = {}
+    for name, rows in (("per head", "1"), ("absorbed", "100000")):
+        monkeypatch.setenv("B2_LATENT_MATERIALISE_ROWS", rows)
+        got[name] = run_schedule(eng, kv, 0, toks, [150, 3, 120, 20])
+        assert close(got[name], ref, dtype), name
+    assert close(got["per head"], got["absorbed"], dtype, tight=True)
 
 
 def test_a_sink_that_dominates_and_one_that_vanishes():
