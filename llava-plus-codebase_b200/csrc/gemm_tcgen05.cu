@@ -127,6 +127,10 @@ struct EpiParams {
     int post = 0;          // fp32 output only: LIN_* activation, scale, accumulate onto the output
     float alpha = 1.f;
     int accumulate = 0;
+    // grouped product (mixture of experts): rows come in tiles of BM that belong to one group each; tile m multiplies with
+    // rows [g * group_rows, (g + 1) * group_rows) of W, g = tile_group[m]; a negative group: the tile is unused and skipped
+    const int* tile_group = nullptr;
+    int group_rows = 0;
 };
 
 __device__ __forceinline__ float act_quick_gelu(float x) { return __fdividef(x, 1.0f + __expf(-1.702f * x)); }
@@ -204,7 +208,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             int stage = 0;
             uint32_t phase = 0;
             int pre_n = 0;
-            if ((int)blockIdx.x < num_tiles) {
+            if ((int)blockIdx.x < num_tiles && ep.tile_group == nullptr) {   // (the group table is made by the upstream kernel)
                 int m_blk, n_blk;
                 tile_coords(blockIdx.x, m_blk, n_blk);
                 for (int kb = 0; kb < num_kb && pre_n < STAGES; ++kb, ++pre_n) {
@@ -218,13 +222,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
                 int m_blk, n_blk;
                 tile_coords(t, m_blk, n_blk);
+                const int grp = ep.tile_group != nullptr ? ep.tile_group[m_blk] : 0;
+                if (grp < 0) continue;
+                const int w_row0 = grp * ep.group_rows;
                 for (int kb = 0; kb < num_kb; ++kb, ++seen) {
                     uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
                     uint8_t* sb = sa + A_TILE_BYTES;
                     if (seen >= pre_n) {
                         mbar_wait(&empty_bar[stage], phase ^ 1);
                         mbar_arrive_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
-                        tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, n_blk * BN, kEvictNormal);
+                        tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * BK, w_row0 + n_blk * BN, kEvictNormal);
                     }
                     tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m_blk * BM, kEvictNormal);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -238,9 +245,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             int stage = 0;
             uint32_t phase = 0;
             int local = 0;
-            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+            if (ep.tile_group != nullptr) pdl_wait();   // the group table comes from the upstream kernel
+            for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+                if (ep.tile_group != nullptr) {
+                    int m_blk, n_blk;
+                    tile_coords(t, m_blk, n_blk);
+                    if (ep.tile_group[m_blk] < 0) continue;
+                }
                 const int as = local & 1;
                 const uint32_t aphase = (local >> 1) & 1;
+                ++local;
                 mbar_wait(&tmem_empty[as], aphase ^ 1);  // epilogue has drained this accumulator
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + as * Cfg::ACC_STRIDE;
@@ -267,11 +281,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int q = warp & 3;            // TMEM lane quadrant this warp may access (warp_id % 4)
         const int half = (warp - 2) >> 2;  // the two warps of a quadrant split the tile's columns
         int local = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
             int m_blk, n_blk;
             tile_coords(t, m_blk, n_blk);
+            if (ep.tile_group != nullptr && ep.tile_group[m_blk] < 0) continue;
             const int as = local & 1;
             const uint32_t aphase = (local >> 1) & 1;
+            ++local;
             mbar_wait(&tmem_full[as], aphase);
             tc_fence_after();
             const int row = m_blk * BM + q * 32 + lane;
@@ -668,7 +684,10 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
                      ((reinterpret_cast<uintptr_t>(g.residual) & 15) == 0 && (g.ld_res % 8) == 0),
                  "gemm: residual must be 16B aligned with ld_res %% 8 == 0");
 
-    if (g.bn_override == 2) return gemm_bf16_2cta(g, stream);  // CTA-pair kernel (cta_group::2, 256x256 pair tiles)
+    const bool grouped = g.tile_group != nullptr;
+    B2_CHECK_ARG(!grouped || (g.groups >= 1 && g.act == ACT_NONE && g.bias == nullptr && g.residual == nullptr && g.M % BM == 0),
+                 "gemm: a grouped product takes whole tiles of %d rows, no bias, residual or fused activation", BM);
+    if (g.bn_override == 2 && !grouped) return gemm_bf16_2cta(g, stream);  // CTA-pair kernel (cta_group::2, 256x256 pair tiles)
 
     // Tile-N choice. Cost model fitted to profiles/r1b_gemm_sweep.json: a tile costs ~BN / rel(BN) (rel = tensor-pipe
     // feed efficiency of the shape: BN=256 needs 96 B/clk of smem operand traffic, BN=128 sits on the 128 B/clk limit,
@@ -691,7 +710,7 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
             const float cost = (float)waves * ((float)cand[i] / rel[i] + 24.f /*per-tile fixed cost*/);
             if (best == 0.f || cost < best) { best = cost; bn = cand[i]; }
         }
-        if (g.bn_override == 0 && g.M >= 512 && g.N >= 256) {
+        if (g.bn_override == 0 && g.M >= 512 && g.N >= 256 && !grouped) {
             const long long pairs = (long long)((g.M + 255) / 256) * ((g.N + 255) / 256);
             const long long pair_slots = num_sms() / 2;
             const long long waves = (pairs + pair_slots - 1) / pair_slots;
@@ -704,8 +723,9 @@ int gemm_bf16(const GemmArgs& g, cudaStream_t stream) {
 
     CUtensorMap ta, tb;
     B2_TRY(make_tmap_bf16(&ta, g.A, g.M, g.K, g.lda, BM));
-    B2_TRY(make_tmap_bf16(&tb, g.W, g.N, g.K, g.ldw, bn));
+    B2_TRY(make_tmap_bf16(&tb, g.W, grouped ? g.N * g.groups : g.N, g.K, g.ldw, bn));
     EpiParams ep;
+    ep.tile_group = g.tile_group; ep.group_rows = g.N;
     ep.bias = reinterpret_cast<const __nv_bfloat16*>(g.bias);
     ep.residual = reinterpret_cast<const __nv_bfloat16*>(g.residual);
     ep.out = g.out;

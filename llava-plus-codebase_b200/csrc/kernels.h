@@ -37,6 +37,9 @@ struct GemmArgs {
     RopeQkv rope;         // ACT_ROPE_QKV only
     // fp32 output only (layer-list decoders): out = alpha * post(acc + bias + residual) (+ out when accumulate); post = LIN_*
     int post = 0; float alpha = 1.f; int accumulate = 0;
+    // grouped product (mixture of experts; single-CTA kernels only): M is a multiple of 128, tile t of 128 rows multiplies with
+    // W rows [g * N, (g + 1) * N), g = tile_group[t] (device; negative: the tile is skipped); W holds `groups` matrices of N rows
+    const int* tile_group = nullptr; int groups = 1;
 };
 int gemm_bf16(const GemmArgs& g, cudaStream_t stream);
 // mm_projector mlp2x_gelu as ONE kernel (gemm_tcgen05.cu, projector_fused_kernel): out = gelu_erf(X W1^T + b1) W2^T + b2.
@@ -322,8 +325,12 @@ int moe_route_f32(const MoeRouteArgs& a, cudaStream_t stream);
 // max_tiles * tile >= rows * top + experts * (tile - 1).
 int moe_plan(const int32_t* idx, int rows, int top, int experts, int tile, int max_tiles, int32_t* pair_pos, int32_t* src_row, int32_t* tile_group,
              cudaStream_t stream);
-// out[r, c] = silu(in[r, c]) * in[r, ff + c], c < ff
-int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t stream);
+// out[r, c] = silu(in[r, c]) * in[r, ff + c], c < ff; out16 (nullable, bf16 [rows, ld_out16]) receives the rounded copy that a
+// tensor-core product reads next (out may then be null)
+int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t stream, void* out16 = nullptr,
+                    int64_t ld_out16 = 0);
+// out[p, :K] = bf16(A[src_row[p], :K]), zeros where src_row[p] < 0: the gathered A operand of a grouped tensor-core product
+int gather_rows_bf16(const float* A, int64_t lda, const int32_t* src_row, void* out, int64_t ld_out, int rows, int K, cudaStream_t stream);
 // x[r] += alpha * sum_k w[r, k] * y[pair_pos[r * top + k]] (pair_pos null: the pair's own index)
 int moe_combine_f32(float* x, const float* y, int64_t ldy, const int32_t* pair_pos, const float* w, int rows, int top, int cols, float alpha,
                     cudaStream_t stream);

@@ -108,12 +108,28 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int32_t* __restric
 }
 
 // out[r, c] = silu(in[r, c]) * in[r, ff + c]
-__global__ void swiglu_rows_kernel(const float* __restrict__ in, int64_t ld_in, float* __restrict__ out, int64_t ld_out, int ff) {
+__global__ void swiglu_rows_kernel(const float* __restrict__ in, int64_t ld_in, float* __restrict__ out, int64_t ld_out, int ff,
+                                   __nv_bfloat16* __restrict__ out16, int64_t ld_out16) {
     const size_t r = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c < ff) {
         const float g = in[r * ld_in + c];
-        out[r * ld_out + c] = g / (1.f + expf(-g)) * in[r * ld_in + ff + c];
+        const float v = g / (1.f + expf(-g)) * in[r * ld_in + ff + c];
+        if (out != nullptr) out[r * ld_out + c] = v;
+        if (out16 != nullptr) out16[r * ld_out16 + c] = __float2bfloat16_rn(v);
+    }
+}
+
+__global__ void gather_rows_bf16_kernel(const float* __restrict__ A, int64_t lda, const int32_t* __restrict__ src_row, __nv_bfloat16* __restrict__ out,
+                                        int64_t ld_out, int K) {
+    const size_t p = blockIdx.y;
+    const int src = src_row[p];
+    const int k = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (k + 1 < K) {
+        const float a = src >= 0 ? A[(size_t)src * lda + k] : 0.f, b = src >= 0 ? A[(size_t)src * lda + k + 1] : 0.f;
+        *reinterpret_cast<__nv_bfloat162*>(out + p * ld_out + k) = __floats2bfloat162_rn(a, b);
+    } else if (k < K) {
+        out[p * ld_out + k] = __float2bfloat16_rn(src >= 0 ? A[(size_t)src * lda + k] : 0.f);
     }
 }
 
@@ -155,9 +171,16 @@ int moe_plan(const int32_t* idx, int rows, int top, int experts, int tile, int m
     return 0;
 }
 
-int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t st) {
-    B2_CHECK_ARG(in && out && rows > 0 && ff > 0, "swiglu_rows: bad argument");
-    swiglu_rows_kernel<<<dim3((ff + 255) / 256, rows), 256, 0, st>>>(in, ld_in, out, ld_out, ff);
+int swiglu_rows_f32(const float* in, int64_t ld_in, float* out, int64_t ld_out, int rows, int ff, cudaStream_t st, void* out16, int64_t ld_out16) {
+    B2_CHECK_ARG(in && (out || out16) && rows > 0 && ff > 0, "swiglu_rows: bad argument");
+    swiglu_rows_kernel<<<dim3((ff + 255) / 256, rows), 256, 0, st>>>(in, ld_in, out, ld_out, ff, reinterpret_cast<__nv_bfloat16*>(out16), ld_out16);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int gather_rows_bf16(const float* A, int64_t lda, const int32_t* src_row, void* out, int64_t ld_out, int rows, int K, cudaStream_t st) {
+    B2_CHECK_ARG(A && src_row && out && rows > 0 && K > 0 && ld_out % 2 == 0, "gather_rows_bf16: bad argument");
+    gather_rows_bf16_kernel<<<dim3((K / 2 + 256) / 256, rows), 256, 0, st>>>(A, lda, src_row, reinterpret_cast<__nv_bfloat16*>(out), ld_out, K);
     B2_LAUNCH_CHECK();
     return 0;
 }

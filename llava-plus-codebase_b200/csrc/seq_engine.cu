@@ -51,7 +51,7 @@ struct SeqModel {
     DevBuf x0;                         // the embedding output, kept for the passes of a looped block
     DevBuf qabs, olat;                 // latent attention: queries carried into the latent space, latent-space outputs [rows, heads*rank]
     DevBuf ffa;                        // activated feed-forward rows
-    DevBuf rlogit, moe_idx, moe_w, moe_pos, moe_src, moe_tile, moe_h, moe_a, moe_y;   // router and grouped expert products
+    DevBuf rlogit, moe_idx, moe_w, moe_pos, moe_src, moe_tile, moe_h, moe_a, moe_y, moe_a16;   // router and grouped expert products
     int lat_w = 0, moe_rows = 0, moe_tiles = 0, moe_hw = 0, moe_aw = 0, moe_top = 0, moe_e = 0;
     std::map<std::string, int> got;
     int w_dtype = DT_BF16;             // dtype of the Linear weights and the embedding table on the device
@@ -328,23 +328,42 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                     ga.out = s.moe_h.as<float>(); ga.ld_out = 2 * ff; ga.N = 2 * ff; ga.K = width; ga.round_a = s.d.compute == B2_COMPUTE_BF16;
                     const int32_t* pos = nullptr;
                     int P = R * top;
+                    const bool tc = ga.round_a && R >= 64 && tc_enabled() && width % 8 == 0 && ff % 8 == 0 && width >= 32 && ff >= 32;
                     if (R <= 8) {
                         ga.tile_rows = 1; ga.tile_group = s.moe_idx.as<int32_t>(); ga.a_div = top; ga.M = P;
                     } else {
-                        const int tiles = (R * top + E * (GROUPED_TILE_ROWS - 1) + GROUPED_TILE_ROWS - 1) / GROUPED_TILE_ROWS;
-                        B2_TRY(moe_plan(s.moe_idx.as<int32_t>(), R, top, E, GROUPED_TILE_ROWS, tiles, s.moe_pos.as<int32_t>(), s.moe_src.as<int32_t>(),
+                        const int tile = tc ? 128 : GROUPED_TILE_ROWS;
+                        const int tiles = (R * top + E * (tile - 1) + tile - 1) / tile;
+                        B2_TRY(moe_plan(s.moe_idx.as<int32_t>(), R, top, E, tile, tiles, s.moe_pos.as<int32_t>(), s.moe_src.as<int32_t>(),
                                         s.moe_tile.as<int32_t>(), st));
                         pos = s.moe_pos.as<int32_t>();
-                        P = tiles * GROUPED_TILE_ROWS;
+                        P = tiles * tile;
                         ga.tile_rows = GROUPED_TILE_ROWS; ga.tile_group = s.moe_tile.as<int32_t>(); ga.a_rows = s.moe_src.as<int32_t>(); ga.M = P;
                     }
-                    B2_TRY(linear_grouped_f32(ga, st));
-                    B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, s.moe_a.as<float>(), ff, P, ff, st));
-                    GroupedLinearArgs gd = ga;
-                    gd.A = s.moe_a.as<float>(); gd.lda = ff; gd.a_rows = nullptr; gd.a_div = 1;
-                    gd.W = W.ed_w.p; gd.ldw = ff; gd.w_group_stride = (int64_t)width * ff;
-                    gd.out = s.moe_y.as<float>(); gd.ld_out = width; gd.N = width; gd.K = ff;
-                    B2_TRY(linear_grouped_f32(gd, st));
+                    if (tc) {
+                        // tensor cores: the sorted pairs' input rows are gathered as bf16, every 128-row tile multiplies with its
+                        // expert's rows of the stacked weight matrices in ONE launch per product
+                        __nv_bfloat16* a16 = s.moe_a16.as<__nv_bfloat16>();
+                        __nv_bfloat16* h16 = a16 + (size_t)s.moe_rows * width;
+                        B2_TRY(gather_rows_bf16(xn, width, s.moe_src.as<int32_t>(), a16, width, P, width, st));
+                        GemmArgs g1;
+                        g1.A = a16; g1.lda = width; g1.W = W.egu_w.p; g1.ldw = width; g1.out = s.moe_h.p; g1.ld_out = 2 * ff; g1.out_fp32 = 1;
+                        g1.M = P; g1.N = 2 * ff; g1.K = width; g1.tile_group = s.moe_tile.as<int32_t>(); g1.groups = E;
+                        B2_TRY(gemm_bf16(g1, st));
+                        B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, nullptr, 0, P, ff, st, h16, ff));
+                        GemmArgs g2;
+                        g2.A = h16; g2.lda = ff; g2.W = W.ed_w.p; g2.ldw = ff; g2.out = s.moe_y.p; g2.ld_out = width; g2.out_fp32 = 1;
+                        g2.M = P; g2.N = width; g2.K = ff; g2.tile_group = s.moe_tile.as<int32_t>(); g2.groups = E;
+                        B2_TRY(gemm_bf16(g2, st));
+                    } else {
+                        B2_TRY(linear_grouped_f32(ga, st));
+                        B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, s.moe_a.as<float>(), ff, P, ff, st));
+                        GroupedLinearArgs gd = ga;
+                        gd.A = s.moe_a.as<float>(); gd.lda = ff; gd.a_rows = nullptr; gd.a_div = 1;
+                        gd.W = W.ed_w.p; gd.ldw = ff; gd.w_group_stride = (int64_t)width * ff;
+                        gd.out = s.moe_y.as<float>(); gd.ld_out = width; gd.N = width; gd.K = ff;
+                        B2_TRY(linear_grouped_f32(gd, st));
+                    }
                     B2_TRY(moe_combine_f32(x, s.moe_y.as<float>(), width, pos, s.moe_w.as<float>(), R, top, width, rm, st));
                 } else {
                     B2_TRY(lin(xn, width, W.up_w, d.ff, width, s.ff.as<float>(), (d.ff + 7) / 8 * 8, R, LIN_RELU_SQ));
@@ -742,7 +761,8 @@ int seq_finalize(b2_model* m) {
     if (moe_e > 0) {
         // (token, choice) pairs sorted by expert, every expert padded to whole tiles
         s.moe_top = moe_top; s.moe_e = moe_e;
-        s.moe_tiles = (int)((R * moe_top + (size_t)moe_e * (GROUPED_TILE_ROWS - 1) + GROUPED_TILE_ROWS - 1) / GROUPED_TILE_ROWS);
+        // (sized for tiles of 128 rows, the tensor-core product's; tiles of 64 pad less)
+        s.moe_tiles = (int)((R * moe_top + (size_t)moe_e * 127 + 127) / 128) * 2;
         s.moe_rows = s.moe_tiles * GROUPED_TILE_ROWS;
         const size_t P = (size_t)s.moe_rows;
         B2_TRY(s.rlogit.alloc(R * router_rows(moe_e) * F4));
@@ -754,6 +774,7 @@ int seq_finalize(b2_model* m) {
         B2_TRY(s.moe_h.alloc(P * 2 * moe_ff * F4));
         B2_TRY(s.moe_a.alloc(P * moe_ff * F4));
         B2_TRY(s.moe_y.alloc(P * width * F4));
+        if (s.d.compute == B2_COMPUTE_BF16) B2_TRY(s.moe_a16.alloc(P * (size_t)(width + moe_ff) * 2));
     }
     {
         int kmax = width;
@@ -783,7 +804,7 @@ void seq_model_free(b2_model* m) {
     }
     DevBuf* bs[] = {&s.embed, &s.head, &s.final_w, &s.final_b, &s.x, &s.proj, &s.act, &s.y, &s.gated, &s.mixout, &s.mixes, &s.rp, &s.wl1, &s.wlog,
                     &s.ff, &s.xn, &s.tok, &s.want, &s.segs, &s.row_slot, &s.row_pos, &s.a16, &s.bigram, &s.loop_step, &s.x0, &s.qabs, &s.olat, &s.ffa,
-                    &s.rlogit, &s.moe_idx, &s.moe_w, &s.moe_pos, &s.moe_src, &s.moe_tile, &s.moe_h, &s.moe_a, &s.moe_y};
+                    &s.rlogit, &s.moe_idx, &s.moe_w, &s.moe_pos, &s.moe_src, &s.moe_tile, &s.moe_h, &s.moe_a, &s.moe_y, &s.moe_a16};
     for (DevBuf* b : bs) b->free();
     delete m->seq;
     m->seq = nullptr;

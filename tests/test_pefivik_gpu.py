@@ -271,6 +271,28 @@ def test_far_keys_and_tile_edges_in_prompts_portions_and_decoding():
     assert err(run_schedule(eng, kv, 0, toks, [300]), ref) < 2e-4, "120 decode steps over split keys"
 
 
+def test_experts_on_tensor_cores_equal_the_plain_products(monkeypatch):
+    """Long bf16 prompt portions sort their (token, choice) pairs by expert into 128-row tiles for ONE grouped tensor-core
+    product per projection; short ones and fp32 use plain grouped products. Uneven expert loads, experts without tokens."""
+    mlp = {"kind": "moe", "expert": {"ff": 40}, "shared": {"ff": 32},
+           "router": {"experts": 12, "top": 3, "groups": {"count": 3, "keep": 2}, "scale": 1.3}}
+    cfg = one_layer(layer(HG_ODD, mlp), width=64)
+    w = O.random_weights(cfg, seed=6)
+    w["l0.mlp.router"][7] = 0.0                       # experts that are (almost) never chosen
+    w["l0.mlp.router"][2] = O.bf16_round(w["l0.mlp.router"][2] * 3.0)
+    model, _ = build(cfg, torch.bfloat16, weights=w, max_seq=512, max_rows=512)
+    eng = model._ensure_engine()
+    kv = eng.new_kv(2, 512)
+    toks = tokens_for(cfg, 330, seed=23)
+    ref, _ = O.forward(cfg, w, toks)
+    got = {}
+    for name, flag in (("tensor cores", "1"), ("plain", "0")):
+        monkeypatch.setenv("B2_SEQ_TC", flag)
+        got[name] = run_schedule(eng, kv, 0, toks, [200, 65, 64])
+        assert close(got[name], ref, torch.bfloat16), name
+    assert close(got["tensor cores"], got["plain"], torch.bfloat16, tight=True)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_absorbed_and_per_head_attention_agree(dtype, monkeypatch):
     """Long prompt portions make per-head keys and values from the cached latent rows; short ones and decode steps carry the
