@@ -341,11 +341,15 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(BiasAttnArgs a) {
     __syncthreads();
     const float inv = inv_s;
     for (int d = threadIdx.x; d < a.dv; d += blockDim.x) {
+        // every split wrote its partial sums (zeros when it had no keys): the loads need no guard and run four at a time
         float acc = 0.f;
-        for (int s = 0; s < a.nsplit; ++s) {
-            const float ws = wgt[s];
-            if (ws != 0.f) acc = fmaf(part[(size_t)s * stride + 2 + d], ws, acc);
+        int s = 0;
+        for (; s + 4 <= a.nsplit; s += 4) {
+            const float p0 = part[(size_t)s * stride + 2 + d], p1 = part[(size_t)(s + 1) * stride + 2 + d];
+            const float p2 = part[(size_t)(s + 2) * stride + 2 + d], p3 = part[(size_t)(s + 3) * stride + 2 + d];
+            acc = fmaf(p0, wgt[s], acc); acc = fmaf(p1, wgt[s + 1], acc); acc = fmaf(p2, wgt[s + 2], acc); acc = fmaf(p3, wgt[s + 3], acc);
         }
+        for (; s < a.nsplit; ++s) acc = fmaf(part[(size_t)s * stride + 2 + d], wgt[s], acc);
         a.out[(size_t)r * a.ldo + (size_t)h * a.dv + d] = acc * inv;
     }
 }
@@ -398,6 +402,7 @@ int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t st) {
         const bool shared_kv = a.vcache == a.kcache;
         const size_t smem = ((size_t)QT * HC * a.dk + (size_t)TL_KT * dkp + (shared_kv ? 0 : (size_t)TL_KT * a.dv)) * sizeof(float);
         dim3 grid((a.rows + QT - 1) / QT, a.G * chunks, a.nsplit);
+        if (a.dv <= 128) return vec ? launch_tile<true, 4>(a, QT, HC, grid, smem, st) : launch_tile<false, 4>(a, QT, HC, grid, smem, st);
         if (a.dv <= 32 * AT_MAXC) return vec ? launch_tile<true, AT_MAXC>(a, QT, HC, grid, smem, st) : launch_tile<false, AT_MAXC>(a, QT, HC, grid, smem, st);
         return vec ? launch_tile<true, 2 * AT_MAXC>(a, QT, HC, grid, smem, st) : launch_tile<false, 2 * AT_MAXC>(a, QT, HC, grid, smem, st);
     }

@@ -184,10 +184,10 @@ int latent_materialise_rows() {  // prompt portions of at least this many rows m
 
 int attn_nsplit(int rows, int G, int max_seq) {
     // a decode step has few (row, key/value head) CTAs: cut the keys so that the step fills the SMs twice over, but keep
-    // at least 64 keys per cut at the cache's capacity
+    // at least 32 keys (one staged tile) per cut at the cache's capacity
     if (rows > 8) return 1;
     int n = (2 * num_sms()) / (rows * G);
-    const int cap = max_seq / 64;
+    const int cap = max_seq / 32;   // a cut is at least one tile of 32 keys
     if (n > cap) n = cap;
     if (n > 64) n = 64;
     return n < 1 ? 1 : n;
