@@ -808,7 +808,7 @@ def pefivik_config(width):
     dense = {"kind": "dense", "ff": 4 * width}
     moe = {"kind": "moe", "expert": {"ff": width // 4}, "shared": {"ff": width // 2},
            "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 2.0}}
-    return {"architecture": "Pefivik", "width": width, "vocab": 32000, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "logit_softcap": 30.0,
+    return {"architecture": "Pefivik", "width": width, "vocab": 32000, "norm": {"eps": 1e-5}, "residual_mult": 0.8, "logit_softcap": 25.0,
             "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 7919}},
             "layers": [dict(lat, mlp=dense), dict(hg, mlp=moe), dict(lat, mlp=moe), dict(hg, mlp=dense)]}
 

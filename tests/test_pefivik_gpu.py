@@ -275,7 +275,7 @@ def test_experts_on_tensor_cores_equal_the_plain_products(monkeypatch):
     """Long bf16 prompt portions sort their (token, choice) pairs by expert into 128-row tiles for ONE grouped tensor-core
     product per projection; short ones and fp32 use plain grouped products. Uneven expert loads, experts without tokens."""
     mlp = {"kind": "moe", "expert": {"ff": 40}, "shared": {"ff": 32},
-           "router": {"experts": 12, "top": 3, "groups": {"count": 3, "keep": 2}, "scale": 1.3}}
+           "router": {"experts": 10, "top": 3, "groups": {"count": 5, "keep": 3}, "scale": 1.3}}
     cfg = one_layer(layer(HG_ODD, mlp), width=64)
     w = O.random_weights(cfg, seed=6)
     w["l0.mlp.router"][7] = 0.0                       # experts that are (almost) never chosen
