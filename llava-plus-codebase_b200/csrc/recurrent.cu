@@ -3,6 +3,8 @@
 // serves a portion of a prompt (n rows of one slot) and a decode step (one row of each of B slots): the rows come as
 // segments (kernels.h, SeqSeg). State, decays, step sizes and sums are fp32; a segment whose pos0 is 0 starts from zero
 // state whatever its slot held before, so a slot that is handed to a new request needs no clearing.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -124,9 +126,9 @@ __global__ void __launch_bounds__(128) token_shift_carry_kernel(const float* __r
 // of its column's state in registers. Tokens are staged TT at a time into shared memory with the per-token preparation done
 // while staging (step size, decay, dt-scaled key), then walked in order with no barrier in between: the recurrence lives in
 // registers, and the KS partial dot products of the tile's tokens meet in shared memory once per tile.
-constexpr int KPT = 16, TT = 16;
+constexpr int TT = 16;   // KPT (template): keys of the state a thread keeps, 16, or 8 for key sizes <= 128 (twice the warps per CTA)
 
-template <int MODE>
+template <int MODE, int KPT>
 __global__ void __launch_bounds__(512) linear_scan_kernel(ScanArgs a) {
     extern __shared__ float sm[];
     const SeqSeg sg = a.segs[blockIdx.z];
@@ -307,28 +309,34 @@ int token_shift_mix_f32(const float* x, const float* mu, float* prev, float* out
     return 0;
 }
 
+template <int MODE, int KPT>
+int launch_scan(const ScanArgs& a, cudaStream_t st) {
+    const int KS = (a.dk + KPT - 1) / KPT;
+    const size_t smem = ((size_t)3 * TT * KS * KPT + TT * 32 + (size_t)TT * KS * 32) * sizeof(float);
+    dim3 grid((a.dv + 31) / 32, a.heads, a.nseg), block(32, KS);
+    if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<MODE, KPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    linear_scan_kernel<MODE, KPT><<<grid, block, smem, st>>>(a);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
 int linear_scan_f32(const ScanArgs& a, cudaStream_t st) {
     B2_CHECK_ARG(a.q && (a.k || a.mode == SCAN_HGRN2) && a.v && a.decay_in && a.state && a.y && a.segs && a.nseg > 0, "linear_scan: null argument");
     B2_CHECK_ARG(a.heads > 0 && a.dk > 0 && a.dv > 0, "linear_scan: bad sizes");
-    const int KS = (a.dk + KPT - 1) / KPT;
-    B2_CHECK_ARG(KS <= 16, "linear_scan: key size %d exceeds %d", a.dk, 16 * KPT);
-    const size_t smem = ((size_t)3 * TT * KS * KPT + TT * 32 + (size_t)TT * KS * 32) * sizeof(float);
-    dim3 grid((a.dv + 31) / 32, a.heads, a.nseg), block(32, KS);
+    B2_CHECK_ARG(a.dk <= 256, "linear_scan: key size %d exceeds 256", a.dk);
+    // 8 keys per thread where 16 key slices cover the key size: twice the warps hide the shared-memory latency of the token walk
+    static const bool narrow_ok = [] { const char* e = getenv("B2_SCAN_KPT8"); return !(e != nullptr && e[0] == '0'); }();
+    const bool narrow = narrow_ok && a.dk <= 128 && a.dk > 16;
     if (a.mode == SCAN_SSD) {
         B2_CHECK_ARG(a.groups > 0 && a.heads % a.groups == 0 && a.dt_bias && a.a_log && a.skip, "linear_scan(ssd): heads %d / groups %d", a.heads, a.groups);
-        if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_SSD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        linear_scan_kernel<SCAN_SSD><<<grid, block, smem, st>>>(a);
-    } else if (a.mode == SCAN_HGRN2) {
-        B2_CHECK_ARG(a.gate_bias && a.gate_lower, "linear_scan(hgrn2): null gate bias / lower bound");
-        if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_HGRN2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        linear_scan_kernel<SCAN_HGRN2><<<grid, block, smem, st>>>(a);
-    } else {
-        B2_CHECK_ARG(a.bonus != nullptr, "linear_scan(rwkv): null bonus");
-        if (smem > 48 * 1024) B2_CUDA_CHECK(cudaFuncSetAttribute(linear_scan_kernel<SCAN_RWKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        linear_scan_kernel<SCAN_RWKV><<<grid, block, smem, st>>>(a);
+        return narrow ? launch_scan<SCAN_SSD, 8>(a, st) : launch_scan<SCAN_SSD, 16>(a, st);
     }
-    B2_LAUNCH_CHECK();
-    return 0;
+    if (a.mode == SCAN_HGRN2) {
+        B2_CHECK_ARG(a.gate_bias && a.gate_lower, "linear_scan(hgrn2): null gate bias / lower bound");
+        return narrow ? launch_scan<SCAN_HGRN2, 8>(a, st) : launch_scan<SCAN_HGRN2, 16>(a, st);
+    }
+    B2_CHECK_ARG(a.bonus != nullptr, "linear_scan(rwkv): null bonus");
+    return narrow ? launch_scan<SCAN_RWKV, 8>(a, st) : launch_scan<SCAN_RWKV, 16>(a, st);
 }
 
 }  // namespace b2
