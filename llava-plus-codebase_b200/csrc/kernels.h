@@ -301,12 +301,14 @@ struct GroupedLinearArgs {
     int M = 0, N = 0, K = 0;
     int act = LIN_NONE;
     int round_a = 0;
+    int swiglu = 0;   // one-row tiles only: a group's matrix is [gate | up] of N rows each and out[m, n] = silu(gate_n . a) * (up_n . a)
 };
 int linear_grouped_f32(const GroupedLinearArgs& g, cudaStream_t stream);
 // `batch` small Linears in one launch on a handful of rows (a decode step's per-head products): for b < batch,
-// out[m, b * o_bs + n] = sum_k A[m, b * a_bs + k] * W[b * w_bs + n * K + k], m < M <= 8; weights in w_dtype, fp32 accumulation
+// out[m, b * o_bs + n] = sum_k A[m, b * a_bs + k] * W[b * w_bs + n * K + k], m < M <= 8; weights in w_dtype, fp32 accumulation;
+// gate (nullable, [M, ldg]): the result is multiplied by sigmoid(gate[m, b])
 int linear_batched_rows_f32(const float* A, int64_t lda, int64_t a_bs, const void* W, int64_t w_bs, int w_dtype, float* out, int64_t ld_out,
-                            int64_t o_bs, int batch, int M, int N, int K, int round_a, cudaStream_t stream);
+                            int64_t o_bs, int batch, int M, int N, int K, int round_a, cudaStream_t stream, const float* gate = nullptr, int64_t ldg = 0);
 enum { GROUPED_TILE_ROWS = 64 };
 
 // ---- mixture of experts (moe.cu) ------------------------------------------------------------------------------------------

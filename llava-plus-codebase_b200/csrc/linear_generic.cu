@@ -318,25 +318,35 @@ __global__ void __launch_bounds__(256) linear_grouped_rows_kernel(GroupedLinearA
     const int n = blockIdx.x * 8 + warp;
     if (n >= g.N) return;
     const TW* w = reinterpret_cast<const TW*>(g.W) + (size_t)grp * g.w_group_stride + (size_t)n * g.ldw;
+    const TW* w2 = w + (size_t)g.N * g.ldw;   // swiglu: the group's matrix is [gate rows | up rows] of N rows each
     const float* a = g.A + (size_t)src * g.lda;
-    float acc = 0.f;
+    float acc = 0.f, acc2 = 0.f;
     if (VEC) {
         for (int k0 = lane * 8; k0 < g.K; k0 += 256) {
-            float wv[8], av[8];
+            float wv[8], av[8], uv[8];
             ld_w8(w + k0, wv);
+            if (g.swiglu) ld_w8(w2 + k0, uv);
             ld_w8(a + k0, av);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc = fmaf(g.round_a ? round_bf16(av[e]) : av[e], wv[e], acc);
+            for (int e = 0; e < 8; ++e) {
+                const float x = g.round_a ? round_bf16(av[e]) : av[e];
+                acc = fmaf(x, wv[e], acc);
+                if (g.swiglu) acc2 = fmaf(x, uv[e], acc2);
+            }
         }
     } else {
         for (int k = lane; k < g.K; k += 32) {
-            const float av = a[k];
-            acc = fmaf(g.round_a ? round_bf16(av) : av, ld_w(w + k), acc);
+            const float av = a[k], x = g.round_a ? round_bf16(av) : av;
+            acc = fmaf(x, ld_w(w + k), acc);
+            if (g.swiglu) acc2 = fmaf(x, ld_w(w2 + k), acc2);
         }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) lin_store(g.out + (size_t)m * g.ld_out + n, acc, nullptr, n, g.act, 1.f, 0);
+    for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xffffffffu, acc, o); acc2 += __shfl_xor_sync(0xffffffffu, acc2, o); }
+    if (lane == 0) {
+        if (g.swiglu) g.out[(size_t)m * g.ld_out + n] = acc / (1.f + expf(-acc)) * acc2;   // silu(gate) * up
+        else lin_store(g.out + (size_t)m * g.ld_out + n, acc, nullptr, n, g.act, 1.f, 0);
+    }
 }
 
 // batched small Linears of a decode step: block = 8 output columns of one batch entry (a head), one warp per column; the
@@ -344,7 +354,7 @@ __global__ void __launch_bounds__(256) linear_grouped_rows_kernel(GroupedLinearA
 template <typename TW, bool VEC>
 __global__ void __launch_bounds__(256) linear_batched_rows_kernel(const float* __restrict__ A, int64_t lda, int64_t a_bs, const TW* __restrict__ W,
                                                                   int64_t w_bs, float* __restrict__ out, int64_t ld_out, int64_t o_bs, int M, int N,
-                                                                  int K, int round_a) {
+                                                                  int K, int round_a, const float* __restrict__ gate, int64_t ldg) {
     const int b = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + warp;
     if (n >= N) return;
@@ -380,19 +390,20 @@ __global__ void __launch_bounds__(256) linear_batched_rows_kernel(const float* _
         float v = acc[m];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && m < M) out[(size_t)m * ld_out + (size_t)b * o_bs + n] = v;
+        // gate: one sigmoid gate per (row, batch entry), e.g. a head's output gate
+        if (lane == 0 && m < M) out[(size_t)m * ld_out + (size_t)b * o_bs + n] = gate != nullptr ? v / (1.f + expf(-gate[(size_t)m * ldg + b])) : v;
     }
 }
 
 template <typename TW>
 int launch_batched_rows(const float* A, int64_t lda, int64_t a_bs, const void* W, int64_t w_bs, float* out, int64_t ld_out, int64_t o_bs, int batch, int M,
-                        int N, int K, int round_a, cudaStream_t st) {
+                        int N, int K, int round_a, const float* gate, int64_t ldg, cudaStream_t st) {
     const bool vec = K % 8 == 0 && lda % 4 == 0 && a_bs % 4 == 0 && w_bs % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
                      (reinterpret_cast<uintptr_t>(W) & 15) == 0;
     dim3 grid((N + 7) / 8, batch);
     const TW* w = reinterpret_cast<const TW*>(W);
-    if (vec) linear_batched_rows_kernel<TW, true><<<grid, 256, 0, st>>>(A, lda, a_bs, w, w_bs, out, ld_out, o_bs, M, N, K, round_a);
-    else linear_batched_rows_kernel<TW, false><<<grid, 256, 0, st>>>(A, lda, a_bs, w, w_bs, out, ld_out, o_bs, M, N, K, round_a);
+    if (vec) linear_batched_rows_kernel<TW, true><<<grid, 256, 0, st>>>(A, lda, a_bs, w, w_bs, out, ld_out, o_bs, M, N, K, round_a, gate, ldg);
+    else linear_batched_rows_kernel<TW, false><<<grid, 256, 0, st>>>(A, lda, a_bs, w, w_bs, out, ld_out, o_bs, M, N, K, round_a, gate, ldg);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -415,16 +426,17 @@ int launch_grouped(const GroupedLinearArgs& g, cudaStream_t st) {
 }  // namespace
 
 int linear_batched_rows_f32(const float* A, int64_t lda, int64_t a_bs, const void* W, int64_t w_bs, int w_dtype, float* out, int64_t ld_out,
-                            int64_t o_bs, int batch, int M, int N, int K, int round_a, cudaStream_t st) {
+                            int64_t o_bs, int batch, int M, int N, int K, int round_a, cudaStream_t st, const float* gate, int64_t ldg) {
     B2_CHECK_ARG(A && W && out && batch > 0 && M > 0 && M <= MR && N > 0 && K > 0, "linear_batched_rows: bad argument (batch=%d M=%d N=%d K=%d)", batch, M, N, K);
     B2_CHECK_ARG(w_dtype == DT_F32 || w_dtype == DT_BF16, "linear_batched_rows: weights must be fp32 or bf16");
-    return w_dtype == DT_F32 ? launch_batched_rows<float>(A, lda, a_bs, W, w_bs, out, ld_out, o_bs, batch, M, N, K, round_a, st)
-                             : launch_batched_rows<__nv_bfloat16>(A, lda, a_bs, W, w_bs, out, ld_out, o_bs, batch, M, N, K, round_a, st);
+    return w_dtype == DT_F32 ? launch_batched_rows<float>(A, lda, a_bs, W, w_bs, out, ld_out, o_bs, batch, M, N, K, round_a, gate, ldg, st)
+                             : launch_batched_rows<__nv_bfloat16>(A, lda, a_bs, W, w_bs, out, ld_out, o_bs, batch, M, N, K, round_a, gate, ldg, st);
 }
 
 int linear_grouped_f32(const GroupedLinearArgs& g, cudaStream_t st) {
     B2_CHECK_ARG(g.A && g.W && g.out && g.tile_group && g.M > 0 && g.N > 0 && g.K > 0, "linear_grouped: bad argument (M=%d N=%d K=%d)", g.M, g.N, g.K);
     B2_CHECK_ARG(g.tile_rows == 1 || g.tile_rows == TB, "linear_grouped: tiles of 1 or %d rows", TB);
+    B2_CHECK_ARG(!g.swiglu || g.tile_rows == 1, "linear_grouped: the gated form is for tiles of one row");
     B2_CHECK_ARG(g.a_rows != nullptr || g.a_div >= 1, "linear_grouped: no source rows");
     B2_CHECK_ARG(g.w_dtype == DT_F32 || g.w_dtype == DT_BF16, "linear_grouped: weights must be fp32 or bf16");
     return g.w_dtype == DT_F32 ? launch_grouped<float>(g, st) : launch_grouped<__nv_bfloat16>(g, st);

@@ -51,7 +51,7 @@ struct SeqModel {
     DevBuf x0;                         // the embedding output, kept for the passes of a looped block
     DevBuf qabs, olat;                 // latent attention: queries carried into the latent space, latent-space outputs [rows, heads*rank]
     DevBuf ffa;                        // activated feed-forward rows
-    DevBuf rlogit, moe_idx, moe_w, moe_pos, moe_src, moe_tile, moe_h, moe_a, moe_y, moe_a16;   // router and grouped expert products
+    DevBuf rlogit, moe_idx, moe_w, moe_pos, moe_src, moe_tile, moe_h, moe_a, moe_y, moe_a16, zero_idx;   // router and grouped expert products
     int lat_w = 0, moe_rows = 0, moe_tiles = 0, moe_hw = 0, moe_aw = 0, moe_top = 0, moe_e = 0;
     std::map<std::string, int> got;
     int w_dtype = DT_BF16;             // dtype of the Linear weights and the embedding table on the device
@@ -273,14 +273,16 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                     aa.nsplit = attn_nsplit(R, (H + 31) / 32, kv->max_seq);
                     if (aa.nsplit > state.nsplit_max) aa.nsplit = state.nsplit_max;
                     B2_TRY(attn_bias_f32(aa, st));
-                    if (R <= 8) {
-                        B2_TRY(linear_batched_rows_f32(s.olat.as<float>(), lq, rank, W.uv_w.p, (int64_t)dv * rank, s.w_dtype, y, L.pv, dv, H, R, dv, rank, round_a, st));
+                    if (R <= 8) {   // with the heads' sigmoid gates in the same launch
+                        y = s.gated.as<float>();
+                        B2_TRY(linear_batched_rows_f32(s.olat.as<float>(), lq, rank, W.uv_w.p, (int64_t)dv * rank, s.w_dtype, y, L.pv, dv, H, R, dv, rank, round_a, st,
+                                                       proj + L.pq + rank, L.pproj_ld));
                     } else {
                         for (int h = 0; h < H; ++h)
                             B2_TRY(lin(s.olat.as<float>() + (size_t)h * rank, lq, W.uv_w, dv, rank, y + (size_t)h * dv, L.pv, R, LIN_NONE, 1.f, 0, nullptr, (size_t)h * dv));
                     }
                 }
-                B2_TRY(head_gate_f32(y, L.pv, proj + L.pq + rank, L.pproj_ld, s.gated.as<float>(), L.pv, R, H, dv, st));
+                if (y != s.gated.as<float>()) B2_TRY(head_gate_f32(y, L.pv, proj + L.pq + rank, L.pproj_ld, s.gated.as<float>(), L.pv, R, H, dv, st));
                 B2_TRY(lin(s.gated.as<float>(), L.pv, W.o_w, width, L.pv, x, width, R, LIN_NONE, rm, 1));
             } else {
                 float* proj = s.proj.as<float>();  // [R, q | f | v]
@@ -317,8 +319,16 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                     B2_TRY(moe_route_f32(ra, st));
                     if (d.moe_shared_ff > 0) {
                         const int sf = d.moe_shared_ff, sfl = (2 * sf + 7) / 8 * 8;
-                        B2_TRY(lin(xn, width, W.sgu_w, 2 * sf, width, s.ff.as<float>(), sfl, R));
-                        B2_TRY(swiglu_rows_f32(s.ff.as<float>(), sfl, s.ffa.as<float>(), sf, R, sf, st));
+                        if (R <= 8) {   // decode step: both projections and the gate in one launch (the shared expert is "group 0" of its matrix)
+                            GroupedLinearArgs gs;
+                            gs.A = xn; gs.lda = width; gs.a_div = 1; gs.W = W.sgu_w.p; gs.ldw = width; gs.w_group_stride = 0; gs.w_dtype = s.w_dtype;
+                            gs.tile_group = s.zero_idx.as<int32_t>(); gs.tile_rows = 1; gs.out = s.ffa.as<float>(); gs.ld_out = sf;
+                            gs.M = R; gs.N = sf; gs.K = width; gs.round_a = s.d.compute == B2_COMPUTE_BF16; gs.swiglu = 1;
+                            B2_TRY(linear_grouped_f32(gs, st));
+                        } else {
+                            B2_TRY(lin(xn, width, W.sgu_w, 2 * sf, width, s.ff.as<float>(), sfl, R));
+                            B2_TRY(swiglu_rows_f32(s.ff.as<float>(), sfl, s.ffa.as<float>(), sf, R, sf, st));
+                        }
                         B2_TRY(lin(s.ffa.as<float>(), sf, W.sd_w, width, sf, x, width, R, LIN_NONE, rm, 1));
                     }
                     // routed experts: (token, choice) pairs as rows of grouped products. A decode step keeps the pairs where
@@ -329,8 +339,9 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                     const int32_t* pos = nullptr;
                     int P = R * top;
                     const bool tc = ga.round_a && R >= 64 && tc_enabled() && width % 8 == 0 && ff % 8 == 0 && width >= 32 && ff >= 32;
-                    if (R <= 8) {
+                    if (R <= 8) {   // decode step: gate, up and the gated activation of a pair in one launch
                         ga.tile_rows = 1; ga.tile_group = s.moe_idx.as<int32_t>(); ga.a_div = top; ga.M = P;
+                        ga.swiglu = 1; ga.N = ff; ga.out = s.moe_a.as<float>(); ga.ld_out = ff;
                     } else {
                         const int tile = tc ? 128 : GROUPED_TILE_ROWS;
                         const int tiles = (R * top + E * (tile - 1) + tile - 1) / tile;
@@ -357,8 +368,9 @@ static int seq_forward(b2_model* m, b2_kv* kv, int R, int nseg, int slot, int ct
                         B2_TRY(gemm_bf16(g2, st));
                     } else {
                         B2_TRY(linear_grouped_f32(ga, st));
-                        B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, s.moe_a.as<float>(), ff, P, ff, st));
+                        if (!ga.swiglu) B2_TRY(swiglu_rows_f32(s.moe_h.as<float>(), 2 * ff, s.moe_a.as<float>(), ff, P, ff, st));
                         GroupedLinearArgs gd = ga;
+                        gd.swiglu = 0;
                         gd.A = s.moe_a.as<float>(); gd.lda = ff; gd.a_rows = nullptr; gd.a_div = 1;
                         gd.W = W.ed_w.p; gd.ldw = ff; gd.w_group_stride = (int64_t)width * ff;
                         gd.out = s.moe_y.as<float>(); gd.ld_out = width; gd.N = width; gd.K = ff;
@@ -774,6 +786,8 @@ int seq_finalize(b2_model* m) {
         B2_TRY(s.moe_h.alloc(P * 2 * moe_ff * F4));
         B2_TRY(s.moe_a.alloc(P * moe_ff * F4));
         B2_TRY(s.moe_y.alloc(P * width * F4));
+        B2_TRY(s.zero_idx.alloc(64 * 4));
+        B2_CUDA_CHECK(cudaMemset(s.zero_idx.p, 0, 64 * 4));
         if (s.d.compute == B2_COMPUTE_BF16) B2_TRY(s.moe_a16.alloc(P * (size_t)(width + moe_ff) * 2));
     }
     {
@@ -804,7 +818,7 @@ void seq_model_free(b2_model* m) {
     }
     DevBuf* bs[] = {&s.embed, &s.head, &s.final_w, &s.final_b, &s.x, &s.proj, &s.act, &s.y, &s.gated, &s.mixout, &s.mixes, &s.rp, &s.wl1, &s.wlog,
                     &s.ff, &s.xn, &s.tok, &s.want, &s.segs, &s.row_slot, &s.row_pos, &s.a16, &s.bigram, &s.loop_step, &s.x0, &s.qabs, &s.olat, &s.ffa,
-                    &s.rlogit, &s.moe_idx, &s.moe_w, &s.moe_pos, &s.moe_src, &s.moe_tile, &s.moe_h, &s.moe_a, &s.moe_y, &s.moe_a16};
+                    &s.rlogit, &s.moe_idx, &s.moe_w, &s.moe_pos, &s.moe_src, &s.moe_tile, &s.moe_h, &s.moe_a, &s.moe_y, &s.moe_a16, &s.zero_idx};
     for (DevBuf* b : bs) b->free();
     delete m->seq;
     m->seq = nullptr;
