@@ -152,8 +152,33 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(BiasAttnArgs a
 // values are the same cached rows (kcache == vcache), the staged key tile is the value tile too. MAXC * 32 >= dv.
 constexpr int TL_KT = 32, TL_WARPS = 8, TL_PPW = 4;
 
+// dst[r * dpitch + c] = src[r * spitch + c] for r < nrows, c < 4 * n4, 16 bytes at a time; a thread issues N loads before its
+// first store, so the copy is bound by bandwidth and not by one memory round trip per element
+template <int N>
+__device__ __forceinline__ void copy_rows_f4(float* __restrict__ dst, int dpitch, const float* __restrict__ src, size_t spitch, int nrows, int n4,
+                                             int tid) {
+    const int total = nrows * n4;
+    for (int base = 0; base < total; base += TL_WARPS * 32 * N) {
+        float4 v[N];
+        int off[N];
+#pragma unroll
+        for (int u = 0; u < N; ++u) {
+            const int e = base + tid + u * TL_WARPS * 32;
+            off[u] = -1;
+            if (e < total) {
+                const int r = e / n4, c = e - r * n4;
+                v[u] = *reinterpret_cast<const float4*>(src + (size_t)r * spitch + c * 4);
+                off[u] = r * dpitch + c * 4;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < N; ++u)
+            if (off[u] >= 0) *reinterpret_cast<float4*>(dst + off[u]) = v[u];
+    }
+}
+
 template <bool VEC, int MAXC>
-__global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a, int QT, int HC) {
+__global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_kernel(BiasAttnArgs a, int QT, int HC) {
     extern __shared__ float sm[];
     const int HGall = a.H / a.G, chunks = (HGall + HC - 1) / HC;
     const int g = blockIdx.y / chunks, h0 = g * HGall + (blockIdx.y % chunks) * HC, HG = min(HC, g * HGall + HGall - h0);
@@ -171,9 +196,15 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
     int maxpos = -1;
     for (int i = 0; i < nrows; ++i) maxpos = max(maxpos, a.row_pos[r0 + i]);
     if (maxpos < 0) return;
-    for (int e = tid; e < P * dk; e += TL_WARPS * 32) {
-        const int p = e / dk, d = e % dk;
-        sQ[e] = a.q[(size_t)(r0 + p / HG) * a.ldq + (size_t)(h0 + p % HG) * dk + d];
+    if (VEC && a.ldq % 4 == 0 && (reinterpret_cast<uintptr_t>(a.q) & 15) == 0) {
+        // a row's heads of this chunk are consecutive in q: HG * dk floats per row, copied 16 bytes at a time
+        for (int i = 0; i < nrows; ++i)
+            copy_rows_f4<4>(sQ + (size_t)i * HG * dk, 0, a.q + (size_t)(r0 + i) * a.ldq + (size_t)h0 * dk, 0, 1, (HG * dk) >> 2, tid);
+    } else {
+        for (int e = tid; e < P * dk; e += TL_WARPS * 32) {
+            const int p = e / dk, d = e % dk;
+            sQ[e] = a.q[(size_t)(r0 + p / HG) * a.ldq + (size_t)(h0 + p % HG) * dk + d];
+        }
     }
     int lo = 0, hi = maxpos + 1;
     if (a.nsplit > 1) {
@@ -186,6 +217,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
     const size_t krs = mat ? (size_t)a.kv_row_stride : (size_t)dk, vrs = mat ? (size_t)a.kv_row_stride_v : (size_t)dv;
     const float* K = mat ? a.kcache + (size_t)g * dk : a.kcache + ((size_t)slot * a.G + g) * a.Smax * dk;
     const float* V = mat ? a.vcache + (size_t)g * dv : a.vcache + ((size_t)slot * a.G + g) * a.Smax * dv;
+    const bool vecv = VEC && dv % 4 == 0 && vrs % 4 == 0 && (reinterpret_cast<uintptr_t>(V) & 15) == 0;   // 16-byte value rows
     float m[TL_PPW], l[TL_PPW], o[TL_PPW][MAXC];
     int ppos[TL_PPW];
 #pragma unroll
@@ -200,16 +232,14 @@ __global__ void __launch_bounds__(TL_WARPS * 32) attn_tile_kernel(BiasAttnArgs a
         const int nk = min(TL_KT, hi - j0);
         __syncthreads();
         if (VEC) {
-            const int dk4 = dk >> 2;
-            for (int e = tid; e < nk * dk4; e += TL_WARPS * 32) {
-                const int kk = e / dk4, d4 = e % dk4;
-                *reinterpret_cast<float4*>(sK + kk * dkp + d4 * 4) = *reinterpret_cast<const float4*>(K + (size_t)(j0 + kk) * krs + d4 * 4);
-            }
+            copy_rows_f4<4>(sK, dkp, K + (size_t)j0 * krs, krs, nk, dk >> 2, tid);
         } else {
             for (int e = tid; e < nk * dk; e += TL_WARPS * 32) sK[(e / dk) * dkp + e % dk] = K[(size_t)(j0 + e / dk) * krs + e % dk];
         }
-        if (!shared_kv)
-            for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)(j0 + e / dv) * vrs + e % dv];
+        if (!shared_kv) {
+            if (vecv) copy_rows_f4<4>(sV, dv, V + (size_t)j0 * vrs, vrs, nk, dv >> 2, tid);
+            else for (int e = tid; e < nk * dv; e += TL_WARPS * 32) sV[e] = V[(size_t)(j0 + e / dv) * vrs + e % dv];
+        }
         __syncthreads();
         // The warp's pairs go through the tile TOGETHER: a lane reads its key row once for all of them, and a value element
         // once per key for all of them (shared-memory bandwidth, not the FMA pipe, limits this loop).
