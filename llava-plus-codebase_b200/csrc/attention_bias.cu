@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, MAXC == 16 ? 1 : 2) attn_tile_k
 
 // one block per (row, head): every thread turns the splits' (max, sum) into weights (nsplit <= 64 values from L1) and combines
 // its value columns in split order
-__global__ void __launch_bounds__(128) attn_merge_kernel(BiasAttnArgs a) {
+__global__ void __launch_bounds__(512) attn_merge_kernel(BiasAttnArgs a) {
     const int w = blockIdx.x;
     const int r = w / a.H, h = w % a.H;
     if (a.row_pos[r] < 0) return;
@@ -409,7 +409,7 @@ int launch_tile(const BiasAttnArgs& a, int QT, int HC, dim3 grid, size_t smem, c
     attn_tile_kernel<VEC, MAXC><<<grid, TL_WARPS * 32, smem, st>>>(a, QT, HC);
     B2_LAUNCH_CHECK();
     if (a.nsplit > 1) {
-        attn_merge_kernel<<<a.rows * a.H, 128, 0, st>>>(a);
+        attn_merge_kernel<<<a.rows * a.H, a.dv > 256 ? 512 : (a.dv > 128 ? 256 : 128), 0, st>>>(a);
         B2_LAUNCH_CHECK();
     }
     return 0;
@@ -443,7 +443,7 @@ int attn_bias_f32(const BiasAttnArgs& a, cudaStream_t st) {
     else attn_bias_kernel<false><<<grid, AT_WARPS * 32, smem, st>>>(a);
     B2_LAUNCH_CHECK();
     if (a.nsplit > 1) {
-        attn_merge_kernel<<<warps, 128, 0, st>>>(a);
+        attn_merge_kernel<<<warps, a.dv > 256 ? 512 : (a.dv > 128 ? 256 : 128), 0, st>>>(a);
         B2_LAUNCH_CHECK();
     }
     return 0;

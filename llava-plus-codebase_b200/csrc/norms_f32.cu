@@ -137,23 +137,50 @@ __global__ void transpose_blocks_kernel(const T* __restrict__ src, T* __restrict
 
 // PolyNorm: out = a N(z) + b N(z^2) + c N(z^3) + e with z = in + bias, powers element-wise, N = division by the row's root mean square
 __global__ void polynorm_kernel(const float* __restrict__ in, int64_t ld_in, const float* __restrict__ bias, const float* __restrict__ coef,
-                                float* __restrict__ out, int64_t ld_out, int cols, float eps) {
+                                float* __restrict__ out, int64_t ld_out, int cols, float eps, int vec) {
     __shared__ float red[33];
     const size_t r = blockIdx.x;
     const float* zr = in + r * ld_in;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-        const float z = zr[c] + (bias != nullptr ? bias[c] : 0.f), z2 = z * z;
-        s2 += z2; s4 = fmaf(z2, z2, s4); s6 = fmaf(z2 * z2, z2, s6);
+    if (vec) {   // 16 bytes at a time, four loads in flight: a decode step has ONE block per row and is bound by memory round trips
+        const float4* z4 = reinterpret_cast<const float4*>(zr);
+        const float4* b4 = reinterpret_cast<const float4*>(bias);
+#pragma unroll 4
+        for (int c = threadIdx.x; c < cols / 4; c += blockDim.x) {
+            float4 z = z4[c];
+            if (bias != nullptr) { const float4 b = b4[c]; z.x += b.x; z.y += b.y; z.z += b.z; z.w += b.w; }
+            const float q0 = z.x * z.x, q1 = z.y * z.y, q2 = z.z * z.z, q3 = z.w * z.w;
+            s2 += (q0 + q1) + (q2 + q3);
+            s4 += fmaf(q0, q0, q1 * q1) + fmaf(q2, q2, q3 * q3);
+            s6 += fmaf(q0 * q0, q0, q1 * q1 * q1) + fmaf(q2 * q2, q2, q3 * q3 * q3);
+        }
+    } else {
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float z = zr[c] + (bias != nullptr ? bias[c] : 0.f), z2 = z * z;
+            s2 += z2; s4 = fmaf(z2, z2, s4); s6 = fmaf(z2 * z2, z2, s6);
+        }
     }
     const float n = (float)cols;
     const float r1 = coef[0] / sqrtf(block_sum(s2, red) / n + eps);
     const float r2 = coef[1] / sqrtf(block_sum(s4, red) / n + eps);
     const float r3 = coef[2] / sqrtf(block_sum(s6, red) / n + eps);
     const float e = coef[3];
-    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-        const float z = zr[c] + (bias != nullptr ? bias[c] : 0.f);
-        out[r * ld_out + c] = fmaf(z, fmaf(z, fmaf(z, r3, r2), r1), e);
+    if (vec) {
+        const float4* z4 = reinterpret_cast<const float4*>(zr);
+        const float4* b4 = reinterpret_cast<const float4*>(bias);
+        float4* o4 = reinterpret_cast<float4*>(out + r * ld_out);
+#pragma unroll 4
+        for (int c = threadIdx.x; c < cols / 4; c += blockDim.x) {
+            float4 z = z4[c];
+            if (bias != nullptr) { const float4 b = b4[c]; z.x += b.x; z.y += b.y; z.z += b.z; z.w += b.w; }
+            o4[c] = make_float4(fmaf(z.x, fmaf(z.x, fmaf(z.x, r3, r2), r1), e), fmaf(z.y, fmaf(z.y, fmaf(z.y, r3, r2), r1), e),
+                                fmaf(z.z, fmaf(z.z, fmaf(z.z, r3, r2), r1), e), fmaf(z.w, fmaf(z.w, fmaf(z.w, r3, r2), r1), e));
+        }
+    } else {
+        for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+            const float z = zr[c] + (bias != nullptr ? bias[c] : 0.f);
+            out[r * ld_out + c] = fmaf(z, fmaf(z, fmaf(z, r3, r2), r1), e);
+        }
     }
 }
 
@@ -193,6 +220,7 @@ __global__ void embed_bigram_kernel(const int32_t* __restrict__ tokens, const Se
     long long brow = buckets;
     if (prev >= 0) brow = (long long)(((unsigned long long)prev * (unsigned long long)mul_prev + (unsigned long long)tok * (unsigned long long)mul_cur) %
                                       (unsigned long long)buckets);
+#pragma unroll 4
     for (int c = threadIdx.x; c < cols; c += blockDim.x) {
         float v = 0.f;
         if (ok) {
@@ -315,7 +343,9 @@ int transpose_blocks(const void* src, void* dst, int blocks, int rows, int cols,
 int polynorm_f32(const float* in, int64_t ld_in, const float* bias, const float* coef, float* out, int64_t ld_out, int rows, int cols, float eps,
                  cudaStream_t st) {
     B2_CHECK_ARG(in && coef && out && rows > 0 && cols > 0, "polynorm: bad argument");
-    polynorm_kernel<<<rows, cols >= 1024 ? 256 : 128, 0, st>>>(in, ld_in, bias, coef, out, ld_out, cols, eps);
+    const int vec = cols % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out) |
+                                                                            reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
+    polynorm_kernel<<<rows, cols >= 4096 ? 512 : (cols >= 1024 ? 256 : 128), 0, st>>>(in, ld_in, bias, coef, out, ld_out, cols, eps, vec);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -341,11 +371,11 @@ int embed_bigram_rows_f32(const int32_t* tokens, const SeqSeg* segs, int nseg, i
     B2_CHECK_ARG(bigram == nullptr || buckets > 0, "embed_bigram_rows: a bigram table needs buckets");
     if (bigram == nullptr) buckets = 1;
     if (table_dtype == DT_F32)
-        embed_bigram_kernel<float><<<dim3(max_n, nseg), 128, 0, st>>>(tokens, segs, reinterpret_cast<const float*>(table),
+        embed_bigram_kernel<float><<<dim3(max_n, nseg), 256, 0, st>>>(tokens, segs, reinterpret_cast<const float*>(table),
                                                                      reinterpret_cast<const float*>(bigram), last_tok, x, x0, cols, vocab, buckets,
                                                                      mul_prev, mul_cur, err_flag);
     else
-        embed_bigram_kernel<__nv_bfloat16><<<dim3(max_n, nseg), 128, 0, st>>>(tokens, segs, reinterpret_cast<const __nv_bfloat16*>(table),
+        embed_bigram_kernel<__nv_bfloat16><<<dim3(max_n, nseg), 256, 0, st>>>(tokens, segs, reinterpret_cast<const __nv_bfloat16*>(table),
                                                                              reinterpret_cast<const __nv_bfloat16*>(bigram), last_tok, x, x0, cols,
                                                                              vocab, buckets, mul_prev, mul_cur, err_flag);
     B2_LAUNCH_CHECK();
